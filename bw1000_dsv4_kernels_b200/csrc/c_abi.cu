@@ -1,0 +1,179 @@
+// extern "C" entry points declared in include/dsv4_w8a8.h: argument checks, then the
+// launchers.  Nothing here allocates, synchronises or touches torch.
+#include <cuda_runtime.h>
+#include <cstdio>
+#include <cstring>
+
+#include "launch_common.h"
+
+namespace w8a8 {
+namespace {
+thread_local char g_last_error[256] = "";
+}
+
+int fail(int code, const char* msg) {
+    std::snprintf(g_last_error, sizeof g_last_error, "%s", msg);
+    return code;
+}
+
+int check_launch(const char* what) {
+    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return 0;
+    std::snprintf(g_last_error, sizeof g_last_error, "%s: %s", what, cudaGetErrorString(e));
+    return DSV4_ERR_LAUNCH;
+}
+
+namespace {
+inline cudaStream_t cs(dsv4_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+int check_rows(const char* op, int M, int N) {
+    if (M < 0 || N < 0) {
+        char msg[128];
+        std::snprintf(msg, sizeof msg, "%s: negative size (M=%d, N=%d)", op, M, N);
+        return fail(DSV4_ERR_ARG, msg);
+    }
+    return 0;
+}
+#define DSV4_REQUIRE_PTR(op, ptr)                                                  \
+    if ((ptr) == nullptr) return fail(DSV4_ERR_ARG, op ": null pointer " #ptr)
+}  // namespace
+}  // namespace w8a8
+
+using namespace w8a8;
+
+extern "C" {
+
+int dsv4_abi_version(void) { return DSV4_ABI_VERSION; }
+
+const char* dsv4_last_error(void) { return g_last_error; }
+
+int dsv4_device_status(dsv4_stream_t stream, int* status_out) { return read_device_status(cs(stream), status_out); }
+
+int launch_ptq_strided(const void* x, int64_t ldx, void* q, void* s, int M, int N, dsv4_stream_t stream) {
+    if (int rc = check_rows("per_token_quant_int8", M, N)) return rc;
+    if (M == 0 || N == 0) return 0;
+    DSV4_REQUIRE_PTR("per_token_quant_int8", x);
+    DSV4_REQUIRE_PTR("per_token_quant_int8", q);
+    DSV4_REQUIRE_PTR("per_token_quant_int8", s);
+    if (ldx < N) return fail(DSV4_ERR_ARG, "per_token_quant_int8: row stride smaller than N");
+    return ptq(x, q, s, M, N, ldx, cs(stream));
+}
+
+int launch_ptq(const void* x, void* q, void* s, int M, int N, dsv4_stream_t stream) {
+    return launch_ptq_strided(x, N, q, s, M, N, stream);
+}
+
+int launch_ptgq(const void* x, void* q, void* s, int M, int N, int gs, dsv4_stream_t stream) {
+    if (int rc = check_rows("per_token_group_quant_int8", M, N)) return rc;
+    if (gs <= 0) return fail(DSV4_ERR_ARG, "per_token_group_quant_int8: group_size must be positive");
+    if (M == 0 || N == 0) return 0;
+    DSV4_REQUIRE_PTR("per_token_group_quant_int8", x);
+    DSV4_REQUIRE_PTR("per_token_group_quant_int8", q);
+    DSV4_REQUIRE_PTR("per_token_group_quant_int8", s);
+    return ptgq(x, q, s, M, N, gs, cs(stream));
+}
+
+int launch_add_rmsnorm_quant(void* res, const void* x, const void* w, void* q, void* s, int M, int N,
+                             float eps, dsv4_stream_t stream) {
+    if (int rc = check_rows("add_rmsnorm_quant", M, N)) return rc;
+    if (M == 0 || N == 0) return 0;
+    DSV4_REQUIRE_PTR("add_rmsnorm_quant", res);
+    DSV4_REQUIRE_PTR("add_rmsnorm_quant", x);
+    DSV4_REQUIRE_PTR("add_rmsnorm_quant", w);
+    DSV4_REQUIRE_PTR("add_rmsnorm_quant", q);
+    DSV4_REQUIRE_PTR("add_rmsnorm_quant", s);
+    return add_rmsnorm_quant(res, x, w, q, s, M, N, eps, cs(stream));
+}
+
+int launch_silu_mul_quant_strided(const void* g, int64_t ldg, const void* u, int64_t ldu, const int* mask,
+                                  void* q, void* s, int M, int N, dsv4_stream_t stream) {
+    if (int rc = check_rows("silu_mul_quant", M, N)) return rc;
+    if (M == 0 || N == 0) return 0;
+    DSV4_REQUIRE_PTR("silu_mul_quant", g);
+    DSV4_REQUIRE_PTR("silu_mul_quant", u);
+    DSV4_REQUIRE_PTR("silu_mul_quant", q);
+    DSV4_REQUIRE_PTR("silu_mul_quant", s);
+    if (ldg < N || ldu < N) return fail(DSV4_ERR_ARG, "silu_mul_quant: row stride smaller than N");
+    return silu_mul_quant(g, u, mask, q, s, M, N, ldg, ldu, cs(stream));
+}
+
+int launch_silu_mul_quant(const void* g, const void* u, void* q, void* s, int M, int N, dsv4_stream_t stream) {
+    return launch_silu_mul_quant_strided(g, N, u, N, nullptr, q, s, M, N, stream);
+}
+
+int launch_silu_mul_masked_quant(const void* g, const void* u, const int* mask, void* q, void* s, int M, int N,
+                                 dsv4_stream_t stream) {
+    return launch_silu_mul_quant_strided(g, N, u, N, mask, q, s, M, N, stream);
+}
+
+int launch_rmsnorm(void* x, int M, int N, float eps, dsv4_stream_t stream) {
+    if (int rc = check_rows("rmsnorm", M, N)) return rc;
+    if (M == 0 || N == 0) return 0;
+    DSV4_REQUIRE_PTR("rmsnorm", x);
+    return rmsnorm(x, M, N, eps, cs(stream));
+}
+
+int launch_rmsnorm_self(void* x, int M, int N, float eps, dsv4_stream_t stream) {
+    return launch_rmsnorm(x, M, N, eps, stream);
+}
+
+int launch_silu_mul(const void* g, const void* u, void* out, int M, int N, dsv4_stream_t stream) {
+    if (int rc = check_rows("silu_and_mul", M, N)) return rc;
+    if (M == 0 || N == 0) return 0;
+    DSV4_REQUIRE_PTR("silu_and_mul", g);
+    DSV4_REQUIRE_PTR("silu_and_mul", u);
+    DSV4_REQUIRE_PTR("silu_and_mul", out);
+    return silu_mul(g, u, out, M, N, N, N, cs(stream));
+}
+
+int launch_w8a8_gemm(const void* A, const void* B, const void* sa, const void* sb, void* C, int M, int N, int K,
+                     dsv4_stream_t stream) {
+    GemmArgs a{};
+    a.A = A; a.B = B; a.sa = static_cast<const float*>(sa); a.sb = static_cast<const float*>(sb); a.C = C;
+    a.offsets = nullptr; a.M = M; a.N = N; a.K = K; a.E = 1; a.sa_groups = 1; a.out_i32 = 0;
+    return gemm_i8(a, cs(stream));
+}
+
+int launch_w8a8_gemm_v5(const void* A, const void* B, const void* sa, const void* sb, void* C, int M, int N,
+                        int K, dsv4_stream_t stream) {
+    return launch_w8a8_gemm(A, B, sa, sb, C, M, N, K, stream);
+}
+
+int launch_w8a8_gemm_i32(const void* A, const void* B, void* C, int M, int N, int K, dsv4_stream_t stream) {
+    GemmArgs a{};
+    a.A = A; a.B = B; a.sa = nullptr; a.sb = nullptr; a.C = C;
+    a.offsets = nullptr; a.M = M; a.N = N; a.K = K; a.E = 1; a.sa_groups = 1; a.out_i32 = 1;
+    return gemm_i8(a, cs(stream));
+}
+
+int launch_scale_convert(const void* int_out, const void* sa, const void* sb, void* bf_out, int M, int N,
+                         dsv4_stream_t stream) {
+    if (int rc = check_rows("scale_convert", M, N)) return rc;
+    if (M == 0 || N == 0) return 0;
+    DSV4_REQUIRE_PTR("scale_convert", int_out);
+    DSV4_REQUIRE_PTR("scale_convert", sa);
+    DSV4_REQUIRE_PTR("scale_convert", sb);
+    DSV4_REQUIRE_PTR("scale_convert", bf_out);
+    return scale_convert(int_out, sa, sb, bf_out, M, N, cs(stream));
+}
+
+int launch_grouped_gemm(const void* A, const void* W, const void* sa, const void* sw, const int* expert_offsets,
+                        void* C, int R, int E, int N, int K, int sa_groups, dsv4_stream_t stream) {
+    if (expert_offsets == nullptr) return fail(DSV4_ERR_ARG, "grouped_gemm: null pointer expert_offsets");
+    GemmArgs a{};
+    a.A = A; a.B = W; a.sa = static_cast<const float*>(sa); a.sb = static_cast<const float*>(sw); a.C = C;
+    a.offsets = expert_offsets; a.M = R; a.N = N; a.K = K; a.E = E; a.sa_groups = sa_groups; a.out_i32 = 0;
+    return gemm_i8(a, cs(stream));
+}
+
+int launch_moe_segments(const int* topk_ids, int T, int topk, int E, int* expert_offsets, int* src_row,
+                        int* dst_slot, dsv4_stream_t stream) {
+    return moe_segments(topk_ids, T, topk, E, expert_offsets, src_row, dst_slot, cs(stream));
+}
+
+int launch_gather_rows(const void* src, const int* src_row, void* dst, int R, int row_bytes,
+                       const float* src_scale, float* dst_scale, int scales_per_row, dsv4_stream_t stream) {
+    return gather_rows(src, src_row, dst, R, row_bytes, src_scale, dst_scale, scales_per_row, cs(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,535 @@
+// W8A8 GEMM for sm_100a: C = bf16((float(A * B^T) * sa) * sb), int8 operands, int32
+// accumulation on the 5th-generation tensor cores.
+//
+//   * A [M,K] and B [N,K] are both K-contiguous, so both MMA operands are "K-major".
+//   * One CTA per SM, persistent over output tiles of 128 x BN.  Warp 0 issues TMA tile
+//     loads (128-byte swizzle, 128 bytes of K per stage) into a ring of shared-memory
+//     stages; warp 1 issues tcgen05.mma.kind::i8 (M128 x BN x K32) from one thread, four
+//     per stage, accumulating in tensor memory; warps 2-5 drain the finished accumulator
+//     with tcgen05.ld, apply the two scales and store bf16.  Tensor memory holds two
+//     accumulators so that the drain of tile i overlaps the MMAs of tile i+1.
+//   * The grouped (MoE) form walks expert segments: the tile list is derived inside the
+//     kernel from expert_offsets (device memory), so no host synchronisation and no
+//     scratch buffer is needed.  Rows of a tile that fall past the end of a segment are
+//     computed and discarded.
+//   * The group-scaled form (one activation scale per 128 of K) cannot defer scaling to
+//     the end: each 128-wide K block is one accumulator that the drain warps fold into
+//     fp32 registers as y = fma(float(acc), sa[row, g], y).
+//   * Every wait on an mbarrier is bounded; a wait that gives up records a code in a
+//     device status word and the CTA leaves its loops and frees its tensor memory.
+//
+// Arithmetic of the epilogue follows hip_kernels/w8a8_gemm_v5.hip:123 and
+// hip_kernels/w8a8_gemm_intmm_fused.hip:34: (float(acc) * sa[row]) * sb[col] -> bf16.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+
+#include "launch_common.h"
+#include "sm100_ptx.cuh"
+#include "w8a8_arith.cuh"
+
+namespace w8a8 {
+
+// Sticky per-device status word written by kernels whose bounded waits ran out.
+__device__ int g_device_status = 0;
+
+namespace {
+
+constexpr int BM = 128;          // tile rows = MMA M = TMEM lanes
+constexpr int BK = 128;          // bytes (= int8 elements) of K per pipeline stage
+constexpr int UMMA_K = 32;       // K per tcgen05.mma for 8-bit operands
+constexpr int kThreads = 192;    // producer warp, MMA warp, four drain warps
+constexpr int kDrainThreads = 128;
+constexpr int kMaxExperts = 1024;
+
+enum WaitSite : int {
+    kWaitEmptyStage = 101,
+    kWaitFullStage = 102,
+    kWaitAccEmpty = 103,
+    kWaitAccFull = 104,
+};
+
+struct Params {
+    const float* sa;
+    const float* sb;
+    void* C;
+    const int* offsets;  // null: dense
+    int M, N, K, E;
+    int sa_groups;
+    int out_i32;
+};
+
+template <int BN, int STAGES>
+struct Smem {
+    static constexpr int kABytes = BM * BK;
+    static constexpr int kBBytes = BN * BK;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTilesBytes = STAGES * kStageBytes;
+    // after the tiles: one copy of the tile's column scales per drain warp, tile prefix,
+    // barriers, tmem slot
+    static constexpr int kSbOff = kTilesBytes;
+    static constexpr int kPrefixOff = kSbOff + 4 * BN * 4;
+    static constexpr int kBarOff = kPrefixOff + (kMaxExperts + 1) * 4 + 4;  // 8-byte aligned below
+    static constexpr int kNumBars = 2 * STAGES + 4;
+    static constexpr int kTmemSlotOff = ((kBarOff + 7) & ~7) + kNumBars * 8;
+    static constexpr int kAbortOff = kTmemSlotOff + 4;
+    static constexpr int kTotal = kAbortOff + 4;
+    static constexpr int kDynamic = kTotal + 1024;  // slack to align the base to 1024
+};
+
+// Maps a linear tile index to (first A row, rows valid, first B row, first C column).
+struct TileCoord {
+    int a_row0;    // first row of A / C
+    int row_end;   // one past the last valid row of this tile's segment
+    int b_row0;    // first row of B (expert * N + n0 for the grouped form)
+    int n0;        // first output column
+    int expert;
+};
+
+struct Scheduler {
+    const Params& p;
+    const int* prefix;  // shared: prefix[e] = m-tiles of experts < e  (grouped only)
+    int tiles_n;
+    int total;
+
+    __device__ Scheduler(const Params& p_, const int* prefix_, int bn) : p(p_), prefix(prefix_) {
+        tiles_n = (p.N + bn - 1) / bn;
+        if (p.offsets == nullptr) {
+            total = ((p.M + BM - 1) / BM) * tiles_n;
+        } else {
+            total = prefix[p.E] * tiles_n;
+        }
+    }
+
+    __device__ TileCoord at(int t, int bn) const {
+        TileCoord c;
+        if (p.offsets == nullptr) {
+            const int tiles_m = (p.M + BM - 1) / BM;
+            const int mt = t % tiles_m, nt = t / tiles_m;
+            c.a_row0 = mt * BM;
+            c.row_end = p.M;
+            c.n0 = nt * bn;
+            c.b_row0 = c.n0;
+            c.expert = 0;
+        } else {
+            // largest e with prefix[e] * tiles_n <= t
+            int lo = 0, hi = p.E;  // invariant: prefix[lo]*tiles_n <= t < prefix[hi]*tiles_n
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (prefix[mid] * tiles_n <= t) lo = mid; else hi = mid;
+            }
+            const int e = lo;
+            const int cnt = prefix[e + 1] - prefix[e];
+            const int local = t - prefix[e] * tiles_n;
+            const int nt = local / cnt, mt = local % cnt;
+            c.a_row0 = p.offsets[e] + mt * BM;
+            c.row_end = p.offsets[e + 1];
+            c.n0 = nt * bn;
+            c.b_row0 = e * p.N + c.n0;
+            c.expert = e;
+        }
+        return c;
+    }
+};
+
+__device__ __forceinline__ void report_wait_failure(int site) {
+    atomicCAS(&g_device_status, 0, site);
+}
+
+// ------------------------------------------------------------------------------------
+// Per-token-scaled (or raw int32) kernel: whole K accumulates in tensor memory.
+// ------------------------------------------------------------------------------------
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const Params p) {
+    using L = Smem<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float* sb_tile = reinterpret_cast<float*>(smem + L::kSbOff);
+    int* prefix = reinterpret_cast<int*>(smem + L::kPrefixOff);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ((L::kBarOff + 7) & ~7));
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlotOff);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
+
+    const uint32_t tiles_base = ptx::smem_u32(smem);
+    const uint32_t bar_base = ptx::smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr uint32_t kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(acc_full_bar(a), 1);
+            ptx::mbar_init(acc_empty_bar(a), kDrainThreads / 32);
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+        ptx::prefetch_tensormap(&tmA);
+        ptx::prefetch_tensormap(&tmB);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    if (p.offsets != nullptr) {
+        // prefix[e] = number of 128-row tiles of the experts before e (warp 2 scans)
+        if (warp == 2) {
+            int carry = 0;
+            for (int e0 = 0; e0 < p.E; e0 += 32) {
+                const int e = e0 + lane;
+                int cnt = 0;
+                if (e < p.E) cnt = (p.offsets[e + 1] - p.offsets[e] + BM - 1) / BM;
+                int incl = cnt;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += v;
+                }
+                if (e < p.E) prefix[e] = carry + incl - cnt;
+                carry += __shfl_sync(0xffffffffu, incl, 31);
+            }
+            if (lane == 0) prefix[p.E] = carry;
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const Scheduler sched(p, prefix, BN);
+    const int k_blocks = (p.K + BK - 1) / BK;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (ptx::elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
+                const TileCoord c = sched.at(t, BN);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u) || *abort_flag) {
+                        report_wait_failure(kWaitEmptyStage);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = tiles_base + stage * L::kStageBytes;
+                    const uint32_t b_dst = a_dst + L::kABytes;
+                    ptx::mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
+                    ptx::tma_load_2d(a_dst, &tmA, kb * BK, c.a_row0, full_bar(stage));
+                    ptx::tma_load_2d(b_dst, &tmB, kb * BK, c.b_row0, full_bar(stage));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (ptx::elect_one()) {
+            constexpr uint32_t idesc = ptx::idesc_i8(BM, BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
+                if (!ptx::mbar_wait_bounded(acc_empty_bar(acc), acc_phase ^ 1u) || *abort_flag) {
+                    report_wait_failure(kWaitAccEmpty);
+                    *abort_flag = 1;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!ptx::mbar_wait_bounded(full_bar(stage), phase) || *abort_flag) {
+                        report_wait_failure(kWaitFullStage);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_src = tiles_base + stage * L::kStageBytes;
+                    const uint64_t adesc = ptx::smem_desc_k_sw128(a_src);
+                    const uint64_t bdesc = ptx::smem_desc_k_sw128(a_src + L::kABytes);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        ptx::mma_i8_ss(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc,
+                                       (kb | k) != 0 ? 1u : 0u);
+                    }
+                    ptx::tc_commit(empty_bar(stage));  // stage reusable once these MMAs retire
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                ptx::tc_commit(acc_full_bar(acc));
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ---------------- drain warps (2..5) ----------------
+        const int quarter = warp & 3;  // TMEM lanes a warp may touch: 32*(warp%4)..+31
+        float* sbs = sb_tile + (warp - 2) * BN;  // private to this warp: no block-level barrier
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        const bool vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+        for (int t = blockIdx.x; t < sched.total; t += gridDim.x) {
+            const TileCoord c = sched.at(t, BN);
+            // column scales of this tile -> this warp's shared copy
+            __syncwarp();
+            if (!p.out_i32) {
+                const float* sb_row = p.sb + (int64_t)c.expert * p.N;
+                for (int j = lane; j < BN; j += 32)
+                    sbs[j] = (c.n0 + j < p.N) ? __ldg(sb_row + c.n0 + j) : 0.0f;
+            }
+            __syncwarp();
+            bool got = ptx::mbar_wait_bounded(acc_full_bar(acc), acc_phase);
+            if (!got || *abort_flag) {
+                report_wait_failure(kWaitAccFull);
+                *abort_flag = 1;
+                break;
+            }
+            ptx::tc_fence_after_sync();
+            const int row = c.a_row0 + quarter * 32 + lane;
+            const bool row_ok = row < c.row_end;
+            const float sa = (row_ok && !p.out_i32) ? __ldg(p.sa + row) : 0.0f;
+            const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                uint32_t r[32];
+                __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the stores
+                ptx::tmem_ld_32x32b_x32(t_lane + cc * 32, r);
+                ptx::tmem_ld_wait();
+                const int n = c.n0 + cc * 32;
+                if (!row_ok || n >= p.N) continue;
+                if (p.out_i32) {
+                    int* out = static_cast<int*>(p.C) + (int64_t)row * p.N + n;
+                    if (vec_ok && n + 32 <= p.N) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<uint4*>(out + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n + j < p.N) out[j] = (int)r[j];
+                    }
+                } else {
+                    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.C) + (int64_t)row * p.N + n;
+                    const float4* sb4 = reinterpret_cast<const float4*>(sbs + cc * 32);
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 s4 = sb4[j];
+                        const float v0 = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 0]), sa), s4.x);
+                        const float v1 = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 1]), sa), s4.y);
+                        const float v2 = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 2]), sa), s4.z);
+                        const float v3 = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 3]), sa), s4.w);
+                        packed[2 * j] = pack_bf16x2_rn(v0, v1);
+                        packed[2 * j + 1] = pack_bf16x2_rn(v2, v3);
+                    }
+                    if (vec_ok && n + 32 <= p.N) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            *reinterpret_cast<uint4*>(out + 8 * j) =
+                                make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const uint32_t w = packed[j >> 1];
+                            const uint16_t h = (j & 1) ? (uint16_t)(w >> 16) : (uint16_t)(w & 0xffffu);
+                            if (n + j < p.N) reinterpret_cast<uint16_t*>(out)[j] = h;
+                        }
+                    }
+                }
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(acc_empty_bar(acc));
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+
+    // ---------------- teardown ----------------
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+// 2-D uint8 tensor [rows, K] (K contiguous), box = 128 bytes of K x box_rows rows,
+// 128-byte swizzle, out-of-range elements read as zero.
+int make_tile_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return fail(DSV4_ERR_DRIVER, "w8a8_gemm: cuTensorMapEncodeTiled is not available");
+    const cuuint64_t dims[2] = {K, rows};
+    const cuuint64_t strides[1] = {K};
+    const cuuint32_t box[2] = {BK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        static thread_local char msg[160];
+        snprintf(msg, sizeof msg, "w8a8_gemm: cuTensorMapEncodeTiled failed with CUresult %d (rows=%llu K=%llu)",
+                 (int)r, (unsigned long long)rows, (unsigned long long)K);
+        return fail(DSV4_ERR_DRIVER, msg);
+    }
+    return 0;
+}
+
+int sm_count() {
+    static thread_local int cached_dev = -1, cached = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (dev != cached_dev) {
+        cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
+        cached_dev = dev;
+    }
+    return cached;
+}
+
+template <int BN, int STAGES>
+int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, int max_tiles,
+                   cudaStream_t st) {
+    using L = Smem<BN, STAGES>;
+    static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
+    // the shared-memory opt-in is per device and per kernel: do it once for each
+    static bool opted_in[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !opted_in[dev]) {
+        if (cudaFuncSetAttribute(gemm_i8_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 L::kDynamic) != cudaSuccess)
+            return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: cannot raise the dynamic shared memory limit");
+        if (dev >= 0 && dev < 64) opted_in[dev] = true;
+    }
+    int grid = sm_count();
+    if (grid <= 0) return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: no CUDA device");
+    if (max_tiles < grid) grid = max_tiles;
+    if (grid < 1) grid = 1;
+    gemm_i8_kernel<BN, STAGES><<<grid, kThreads, L::kDynamic, st>>>(tmA, tmB, p);
+    return check_launch("w8a8_gemm");
+}
+
+}  // namespace
+
+int gemm_i8(const GemmArgs& a, cudaStream_t st) {
+    const bool grouped = a.offsets != nullptr;
+    if (a.M < 0 || a.N < 0 || a.K < 0) return fail(DSV4_ERR_ARG, "w8a8_gemm: negative size");
+    if (a.M == 0 || a.N == 0) return 0;
+    if (a.K == 0) return fail(DSV4_ERR_ARG, "w8a8_gemm: K must be positive");
+    if (a.A == nullptr || a.B == nullptr || a.C == nullptr) return fail(DSV4_ERR_ARG, "w8a8_gemm: null pointer");
+    if (!a.out_i32 && (a.sa == nullptr || a.sb == nullptr)) return fail(DSV4_ERR_ARG, "w8a8_gemm: null scale pointer");
+    if (a.K % 16 != 0) return fail(DSV4_ERR_ARG, "w8a8_gemm: K must be a multiple of 16 (TMA row stride)");
+    if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15))
+        return fail(DSV4_ERR_ARG, "w8a8_gemm: A and B must be 16-byte aligned");
+    if (grouped && (a.E <= 0 || a.E > kMaxExperts)) return fail(DSV4_ERR_ARG, "grouped_gemm: E must be in 1..1024");
+    if (a.sa_groups != 1) return fail(DSV4_ERR_ARG, "grouped_gemm: this build supports per-token scales only");
+
+    Params p;
+    p.sa = a.sa; p.sb = a.sb; p.C = a.C; p.offsets = a.offsets;
+    p.M = a.M; p.N = a.N; p.K = a.K; p.E = grouped ? a.E : 1;
+    p.sa_groups = a.sa_groups; p.out_i32 = a.out_i32;
+
+    const uint64_t b_rows = grouped ? (uint64_t)a.E * a.N : (uint64_t)a.N;
+    const int sms = sm_count();
+    const int tiles_m_bound = grouped ? (a.M / BM + a.E) : (a.M + BM - 1) / BM;
+
+    // Tile width: 256 columns when that already gives every SM a tile, otherwise narrower
+    // tiles so that a short, weight-streaming problem spreads over more SMs.
+    int bn = 256;
+    if ((int64_t)tiles_m_bound * ((a.N + 255) / 256) < sms) bn = 128;
+    if (bn == 128 && (int64_t)tiles_m_bound * ((a.N + 127) / 128) < sms) bn = 64;
+    if (bn == 64 && (int64_t)tiles_m_bound * ((a.N + 63) / 64) < sms) bn = 32;
+
+    CUtensorMap tmA, tmB;
+    int rc = make_tile_map(&tmA, a.A, (uint64_t)a.M, (uint64_t)a.K, BM);
+    if (rc) return rc;
+    rc = make_tile_map(&tmB, a.B, b_rows, (uint64_t)a.K, (uint32_t)bn);
+    if (rc) return rc;
+    const int max_tiles = tiles_m_bound * ((a.N + bn - 1) / bn);
+    switch (bn) {
+        case 256: return launch_variant<256, 4>(tmA, tmB, p, max_tiles, st);
+        case 128: return launch_variant<128, 6>(tmA, tmB, p, max_tiles, st);
+        case 64: return launch_variant<64, 8>(tmA, tmB, p, max_tiles, st);
+        default: return launch_variant<32, 10>(tmA, tmB, p, max_tiles, st);
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// int32 [M,N] -> bf16 with the two scales (hip_kernels/w8a8_gemm_intmm_fused.hip:22-36)
+// ------------------------------------------------------------------------------------
+namespace {
+__global__ void __launch_bounds__(256) scale_convert_kernel(const int* __restrict__ acc,
+                                                            const float* __restrict__ sa,
+                                                            const float* __restrict__ sb,
+                                                            __nv_bfloat16* __restrict__ out, int M, int N) {
+    const int64_t total = (int64_t)M * N;
+    for (int64_t f = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; f < total;
+         f += (int64_t)gridDim.x * blockDim.x) {
+        const int row = (int)(f / N), col = (int)(f % N);
+        out[f] = __float2bfloat16_rn(__fmul_rn(__fmul_rn(__int2float_rn(acc[f]), sa[row]), sb[col]));
+    }
+}
+}  // namespace
+
+int scale_convert(const void* acc, const void* sa, const void* sb, void* out, int M, int N, cudaStream_t st) {
+    if (M == 0 || N == 0) return 0;
+    int64_t blocks = ((int64_t)M * N + 255) / 256;
+    if (blocks > (1 << 20)) blocks = 1 << 20;
+    scale_convert_kernel<<<(int)blocks, 256, 0, st>>>(static_cast<const int*>(acc), static_cast<const float*>(sa),
+                                                      static_cast<const float*>(sb),
+                                                      static_cast<__nv_bfloat16*>(out), M, N);
+    return check_launch("scale_convert");
+}
+
+int read_device_status(cudaStream_t st, int* out) {
+    if (cudaStreamSynchronize(st) != cudaSuccess) return fail(DSV4_ERR_LAUNCH, "device_status: stream synchronise failed");
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess)
+        return fail(DSV4_ERR_LAUNCH, "device_status: cannot read the status word");
+    if (v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+    }
+    if (out) *out = v;
+    return 0;
+}
+
+}  // namespace w8a8

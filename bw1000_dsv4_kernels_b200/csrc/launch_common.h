@@ -1,0 +1,49 @@
+// Status codes and error reporting shared by the launchers behind the C-ABI.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "../../include/dsv4_w8a8.h"
+
+namespace w8a8 {
+
+// Records `msg` as the calling thread's last error and returns `code`.
+int fail(int code, const char* msg);
+// cudaGetLastError() after a launch; records "<what>: <cuda error string>" on failure.
+int check_launch(const char* what);
+
+// ---- launchers implemented in rowwise_quant.cu -----------------------------------
+int ptq(const void* x, void* q, void* s, int M, int K, int64_t ldx, cudaStream_t st);
+int ptgq(const void* x, void* q, void* s, int M, int K, int gs, cudaStream_t st);
+int add_rmsnorm_quant(void* res, const void* x, const void* w, void* q, void* s, int M, int K,
+                      float eps, cudaStream_t st);
+int rmsnorm(void* x, int M, int K, float eps, cudaStream_t st);
+int silu_mul_quant(const void* g, const void* u, const int* mask, void* q, void* s, int M, int N,
+                   int64_t ldg, int64_t ldu, cudaStream_t st);
+int silu_mul(const void* g, const void* u, void* out, int M, int N, int64_t ldg, int64_t ldu,
+             cudaStream_t st);
+
+// ---- launchers implemented in gemm_i8_sm100.cu ------------------------------------
+struct GemmArgs {
+    const void* A;        // int8 [M or R, K]
+    const void* B;        // int8 [N, K] or [E, N, K]
+    const float* sa;      // [M] per token, or [M, K/128] when sa_groups > 1
+    const float* sb;      // [N] or [E, N]; may be null only when out_i32
+    void* C;              // bf16 [M, N] or int32 [M, N]
+    const int* offsets;   // null for a dense GEMM, else expert_offsets[E+1]
+    int M, N, K, E;
+    int sa_groups;        // 1 = per-token scale; K/128 = one scale per 128 of K
+    int out_i32;          // 1 = write raw int32 accumulators
+};
+int gemm_i8(const GemmArgs& a, cudaStream_t st);
+int scale_convert(const void* acc, const void* sa, const void* sb, void* out, int M, int N,
+                  cudaStream_t st);
+
+// ---- launchers implemented in moe_segments.cu -------------------------------------
+int moe_segments(const int* topk_ids, int T, int topk, int E, int* offsets, int* src_row,
+                 int* dst_slot, cudaStream_t st);
+int gather_rows(const void* src, const int* src_row, void* dst, int R, int row_bytes,
+                const float* src_scale, float* dst_scale, int scales_per_row, cudaStream_t st);
+int read_device_status(cudaStream_t st, int* out);
+
+}  // namespace w8a8

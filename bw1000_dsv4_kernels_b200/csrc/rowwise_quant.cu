@@ -1,0 +1,664 @@
+// Row-wise activation kernels of the W8A8 path: per-token and per-group int8
+// quantisers, residual-add + RMSNorm + quantise, SiLU*up + quantise, and the two
+// unfused neighbours (rmsnorm, silu_and_mul).
+//
+// All of them are HBM-bound.  The fast kernels read each row once with 128-bit
+// loads (8 bf16 per load), keep the row in registers between the reduction and
+// the store, reduce with warp shuffles, and write int8 codes as 64-bit stores.
+// A row is owned by one CTA; vector v of a row (elements 8v..8v+7) belongs to
+// thread v mod blockDim.  The *_generic kernels accept any K and any alignment
+// with scalar accesses and produce the same bits.
+//
+// Sum-of-squares order (add_rmsnorm_quant, rmsnorm): always 256 lanes.  Lane l
+// accumulates its vectors v = l, l+256, ... in increasing v, and the 8 elements
+// of a vector in increasing index, as acc = acc + a*a (separately rounded).  The
+// 256 partials are reduced by an xor butterfly inside each group of 32 lanes and
+// the 8 group sums are added left to right.  The order depends on K only.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+
+#include "w8a8_arith.cuh"
+#include "launch_common.h"
+
+namespace w8a8 {
+
+constexpr int kSumLanes = 256;
+
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ld_plain(const uint4* p) { return *p; }
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    f[0] = bf16lo_to_f32(v.x); f[1] = bf16hi_to_f32(v.x);
+    f[2] = bf16lo_to_f32(v.y); f[3] = bf16hi_to_f32(v.y);
+    f[4] = bf16lo_to_f32(v.z); f[5] = bf16hi_to_f32(v.z);
+    f[6] = bf16lo_to_f32(v.w); f[7] = bf16hi_to_f32(v.w);
+}
+
+__device__ __forceinline__ uint2 quant8_rn(const float (&f)[8], float inv) {
+    uint2 o;
+    o.x = pack_i8x4(quant_rn(f[0], inv), quant_rn(f[1], inv), quant_rn(f[2], inv), quant_rn(f[3], inv));
+    o.y = pack_i8x4(quant_rn(f[4], inv), quant_rn(f[5], inv), quant_rn(f[6], inv), quant_rn(f[7], inv));
+    return o;
+}
+
+// max |.| of the 8 bf16 in a 16-byte vector, done on packed bf16 pairs (exact)
+__device__ __forceinline__ __nv_bfloat162 absmax_bf16x8(__nv_bfloat162 m, const uint4& v) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) m = __hmax2(m, __habs2(p[i]));
+    return m;
+}
+
+// Block-wide max.  `red` has one slot per warp.  Every thread returns the result.
+__device__ __forceinline__ float block_max(float v, float* red) {
+    v = warp_max(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float m = (lane < nwarps) ? red[lane] : 0.0f;
+    return warp_max(m);
+}
+
+// Block-wide sum over exactly 256 threads in the fixed order described on top.
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+    v = warp_sum_butterfly(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = red[0];
+#pragma unroll
+    for (int w = 1; w < kSumLanes / 32; ++w) t = __fadd_rn(t, red[w]);
+    return t;
+}
+
+// ====================================================================================
+// per_token_quant_int8  (reference: hip_kernels/dsv4_native_ext.cpp:24-40)
+// ====================================================================================
+template <int VPT>
+__global__ void __launch_bounds__(1024) ptq_vec_kernel(const __nv_bfloat16* __restrict__ x,
+                                                       int8_t* __restrict__ q,
+                                                       float* __restrict__ s, int M, int K,
+                                                       int64_t ldx) {
+    __shared__ float red[32];
+    const int V = K >> 3, T = blockDim.x, tid = threadIdx.x;
+    for (int row = blockIdx.x; row < M; row += gridDim.x) {
+        const uint4* xr = reinterpret_cast<const uint4*>(x + (int64_t)row * ldx);
+        uint4 v[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int idx = tid + i * T;
+            v[i] = (idx < V) ? ld_stream(xr + idx) : make_uint4(0, 0, 0, 0);
+        }
+        __nv_bfloat162 m2 = __float2bfloat162_rn(0.0f);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) m2 = absmax_bf16x8(m2, v[i]);
+        float am = fmaxf(__low2float(m2), __high2float(m2));
+        am = block_max(am, red);
+        float scale, inv;
+        scale_from_amax(am, scale, inv);
+        if (tid == 0) s[row] = scale;
+        uint2* qr = reinterpret_cast<uint2*>(q + (int64_t)row * K);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int idx = tid + i * T;
+            if (idx < V) {
+                float f[8];
+                unpack8(v[i], f);
+                qr[idx] = quant8_rn(f, inv);
+            }
+        }
+        __syncthreads();  // `red` is reused by the next row
+    }
+}
+
+// any K, any alignment; two reads of the row
+__global__ void __launch_bounds__(256) ptq_generic_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          int8_t* __restrict__ q,
+                                                          float* __restrict__ s, int M, int K,
+                                                          int64_t ldx) {
+    __shared__ float red[32];
+    for (int row = blockIdx.x; row < M; row += gridDim.x) {
+        const __nv_bfloat16* xr = x + (int64_t)row * ldx;
+        float am = 0.0f;
+        for (int j = threadIdx.x; j < K; j += blockDim.x) am = fmaxf(am, fabsf(__bfloat162float(xr[j])));
+        am = block_max(am, red);
+        float scale, inv;
+        scale_from_amax(am, scale, inv);
+        if (threadIdx.x == 0) s[row] = scale;
+        int8_t* qr = q + (int64_t)row * K;
+        for (int j = threadIdx.x; j < K; j += blockDim.x)
+            qr[j] = (int8_t)quant_rn(__bfloat162float(xr[j]), inv);
+        __syncthreads();
+    }
+}
+
+// ====================================================================================
+// per_token_group_quant_int8  (reference: hip_kernels/dsv4_all_hip_kernels.hip:49-86)
+// Flat over all 16-byte vectors of a contiguous [M,K] tensor: vector f belongs to
+// group f / LPG where LPG = group_size/8 lanes cooperate through shuffles.
+// ====================================================================================
+template <int LPG, int UNROLL>
+__global__ void __launch_bounds__(256) ptgq_vec_kernel(const uint4* __restrict__ x,
+                                                       uint2* __restrict__ q,
+                                                       float* __restrict__ s, int64_t nvec) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t base = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; base < nvec;
+         base += stride * UNROLL) {
+        uint4 v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int64_t f = base + u * stride;
+            v[u] = (f < nvec) ? ld_stream(x + f) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int64_t f = base + u * stride;
+            __nv_bfloat162 m2 = absmax_bf16x8(__float2bfloat162_rn(0.0f), v[u]);
+            float am = fmaxf(__low2float(m2), __high2float(m2));
+            // nvec is a multiple of LPG and stride a multiple of 32, so the LPG lanes of
+            // a group are all in range or all out of range together
+#pragma unroll
+            for (int o = LPG / 2; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+            if (f < nvec) {
+                const float scale = __fdiv_rn(fmaxf(am, kAmaxFloor), 127.0f);
+                if ((threadIdx.x & (LPG - 1)) == 0) s[f / LPG] = scale;
+                float e[8];
+                unpack8(v[u], e);
+                uint2 o2;
+                o2.x = pack_i8x4(quant_trunc_div(e[0], scale), quant_trunc_div(e[1], scale),
+                                 quant_trunc_div(e[2], scale), quant_trunc_div(e[3], scale));
+                o2.y = pack_i8x4(quant_trunc_div(e[4], scale), quant_trunc_div(e[5], scale),
+                                 quant_trunc_div(e[6], scale), quant_trunc_div(e[7], scale));
+                q[f] = o2;
+            }
+        }
+    }
+}
+
+// one warp per (row, group); any group size, ragged last group allowed.
+// Scales are laid out [M, ceil(K/gs)].
+__global__ void __launch_bounds__(256) ptgq_generic_kernel(const __nv_bfloat16* __restrict__ x,
+                                                           int8_t* __restrict__ q,
+                                                           float* __restrict__ s, int M, int K,
+                                                           int gs, int64_t ldx) {
+    const int G = (K + gs - 1) / gs;
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < (int64_t)M * G; w += warps) {
+        const int row = (int)(w / G), g = (int)(w % G);
+        const int j0 = g * gs, j1 = min(j0 + gs, K);
+        const __nv_bfloat16* xr = x + (int64_t)row * ldx;
+        float am = 0.0f;
+        for (int j = j0 + lane; j < j1; j += 32) am = fmaxf(am, fabsf(__bfloat162float(xr[j])));
+        am = warp_max(am);
+        const float scale = __fdiv_rn(fmaxf(am, kAmaxFloor), 127.0f);
+        if (lane == 0) s[(int64_t)row * G + g] = scale;
+        int8_t* qr = q + (int64_t)row * K;
+        for (int j = j0 + lane; j < j1; j += 32)
+            qr[j] = (int8_t)quant_trunc_div(__bfloat162float(xr[j]), scale);
+    }
+}
+
+// ====================================================================================
+// add_rmsnorm_quant  (reference: hip_kernels/dsv4_native_ext.cpp:103-132)
+// 256 threads per row, VPT vectors per thread held in registers as fp32.
+// ====================================================================================
+template <int VPT>
+__global__ void __launch_bounds__(kSumLanes) add_rmsnorm_quant_vec_kernel(
+    __nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ x,
+    const __nv_bfloat16* __restrict__ w, int8_t* __restrict__ q, float* __restrict__ s, int M,
+    int K, float eps) {
+    __shared__ float red_sum[8];
+    __shared__ float red_max[32];
+    const int V = K >> 3, tid = threadIdx.x;
+    for (int row = blockIdx.x; row < M; row += gridDim.x) {
+        uint4* rr = reinterpret_cast<uint4*>(res + (int64_t)row * K);
+        const uint4* xr = reinterpret_cast<const uint4*>(x + (int64_t)row * K);
+        const uint4* wr = reinterpret_cast<const uint4*>(w);
+        uint4 rv[VPT], xv[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int idx = tid + i * kSumLanes;
+            if (idx < V) {
+                rv[i] = ld_plain(rr + idx);  // written back below: keep it on the coherent path
+                xv[i] = ld_stream(xr + idx);
+            } else {
+                rv[i] = make_uint4(0, 0, 0, 0);
+                xv[i] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        float a[VPT][8];
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            float r8[8], x8[8];
+            unpack8(rv[i], r8);
+            unpack8(xv[i], x8);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                a[i][e] = __fadd_rn(r8[e], x8[e]);
+                ss = __fadd_rn(ss, __fmul_rn(a[i][e], a[i][e]));
+            }
+            const int idx = tid + i * kSumLanes;
+            if (idx < V) {
+                uint4 o;
+                o.x = pack_bf16x2_rn(a[i][0], a[i][1]);
+                o.y = pack_bf16x2_rn(a[i][2], a[i][3]);
+                o.z = pack_bf16x2_rn(a[i][4], a[i][5]);
+                o.w = pack_bf16x2_rn(a[i][6], a[i][7]);
+                rr[idx] = o;
+            }
+        }
+        const float total = block_sum_256(ss, red_sum);
+        const float rrms = rrms_from_sumsq(total, K, eps);
+        float am = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int idx = tid + i * kSumLanes;
+            float w8[8];
+            const uint4 wv = (idx < V) ? __ldg(wr + idx) : make_uint4(0, 0, 0, 0);
+            unpack8(wv, w8);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                a[i][e] = __fmul_rn(__fmul_rn(a[i][e], rrms), w8[e]);
+                am = fmaxf(am, fabsf(a[i][e]));
+            }
+        }
+        am = block_max(am, red_max);
+        float scale, inv;
+        scale_from_amax(am, scale, inv);
+        if (tid == 0) s[row] = scale;
+        uint2* qr = reinterpret_cast<uint2*>(q + (int64_t)row * K);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int idx = tid + i * kSumLanes;
+            if (idx < V) qr[idx] = quant8_rn(a[i], inv);
+        }
+        __syncthreads();
+    }
+}
+
+// Element j of a row belongs to lane (j/8) mod 256; a lane walks its elements in
+// increasing j.  Used by the *_generic kernels so that their sums associate exactly
+// like the vector kernels'.
+#define W8A8_FOR_LANE_ELEMENTS(j, K)                                              \
+    for (int _v = threadIdx.x; _v * 8 < (K); _v += kSumLanes)                     \
+        for (int j = _v * 8; j < min(_v * 8 + 8, (K)); ++j)
+
+__global__ void __launch_bounds__(kSumLanes) add_rmsnorm_quant_generic_kernel(
+    __nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ x,
+    const __nv_bfloat16* __restrict__ w, int8_t* __restrict__ q, float* __restrict__ s, int M,
+    int K, float eps) {
+    __shared__ float red_sum[8];
+    __shared__ float red_max[32];
+    for (int row = blockIdx.x; row < M; row += gridDim.x) {
+        __nv_bfloat16* rr = res + (int64_t)row * K;
+        const __nv_bfloat16* xr = x + (int64_t)row * K;
+        float ss = 0.0f;
+        W8A8_FOR_LANE_ELEMENTS(j, K) {
+            const float a = __fadd_rn(__bfloat162float(rr[j]), __bfloat162float(xr[j]));
+            ss = __fadd_rn(ss, __fmul_rn(a, a));
+        }
+        const float rrms = rrms_from_sumsq(block_sum_256(ss, red_sum), K, eps);
+        float am = 0.0f;
+        W8A8_FOR_LANE_ELEMENTS(j, K) {
+            const float a = __fadd_rn(__bfloat162float(rr[j]), __bfloat162float(xr[j]));
+            const float y = __fmul_rn(__fmul_rn(a, rrms), __bfloat162float(w[j]));
+            am = fmaxf(am, fabsf(y));
+        }
+        am = block_max(am, red_max);
+        float scale, inv;
+        scale_from_amax(am, scale, inv);
+        if (threadIdx.x == 0) s[row] = scale;
+        int8_t* qr = q + (int64_t)row * K;
+        W8A8_FOR_LANE_ELEMENTS(j, K) {
+            const float a = __fadd_rn(__bfloat162float(rr[j]), __bfloat162float(xr[j]));
+            const float y = __fmul_rn(__fmul_rn(a, rrms), __bfloat162float(w[j]));
+            qr[j] = (int8_t)quant_rn(y, inv);
+            rr[j] = __float2bfloat16_rn(a);  // last use of the old residual value
+        }
+        __syncthreads();
+    }
+}
+
+// ====================================================================================
+// rmsnorm, in place, no gamma  (reference: hip_kernels/dsv4_native_ext.cpp:45-60)
+// ====================================================================================
+template <int VPT>
+__global__ void __launch_bounds__(kSumLanes) rmsnorm_vec_kernel(__nv_bfloat16* __restrict__ x, int M,
+                                                                int K, float eps) {
+    __shared__ float red_sum[8];
+    const int V = K >> 3, tid = threadIdx.x;
+    for (int row = blockIdx.x; row < M; row += gridDim.x) {
+        uint4* xr = reinterpret_cast<uint4*>(x + (int64_t)row * K);
+        float a[VPT][8];
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int idx = tid + i * kSumLanes;
+            const uint4 v = (idx < V) ? ld_plain(xr + idx) : make_uint4(0, 0, 0, 0);
+            unpack8(v, a[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < VPT; ++i)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = __fadd_rn(ss, __fmul_rn(a[i][e], a[i][e]));
+        const float rrms = rrms_from_sumsq(block_sum_256(ss, red_sum), K, eps);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int idx = tid + i * kSumLanes;
+            if (idx < V) {
+                uint4 o;
+                o.x = pack_bf16x2_rn(__fmul_rn(a[i][0], rrms), __fmul_rn(a[i][1], rrms));
+                o.y = pack_bf16x2_rn(__fmul_rn(a[i][2], rrms), __fmul_rn(a[i][3], rrms));
+                o.z = pack_bf16x2_rn(__fmul_rn(a[i][4], rrms), __fmul_rn(a[i][5], rrms));
+                o.w = pack_bf16x2_rn(__fmul_rn(a[i][6], rrms), __fmul_rn(a[i][7], rrms));
+                xr[idx] = o;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+__global__ void __launch_bounds__(kSumLanes) rmsnorm_generic_kernel(__nv_bfloat16* __restrict__ x,
+                                                                    int M, int K, float eps) {
+    __shared__ float red_sum[8];
+    for (int row = blockIdx.x; row < M; row += gridDim.x) {
+        __nv_bfloat16* xr = x + (int64_t)row * K;
+        float ss = 0.0f;
+        W8A8_FOR_LANE_ELEMENTS(j, K) {
+            const float a = __bfloat162float(xr[j]);
+            ss = __fadd_rn(ss, __fmul_rn(a, a));
+        }
+        const float rrms = rrms_from_sumsq(block_sum_256(ss, red_sum), K, eps);
+        W8A8_FOR_LANE_ELEMENTS(j, K) {
+            xr[j] = __float2bfloat16_rn(__fmul_rn(__bfloat162float(xr[j]), rrms));
+        }
+        __syncthreads();
+    }
+}
+
+// ====================================================================================
+// silu_mul_quant (+ optional row mask)
+// (reference: hip_kernels/dsv4_native_ext.cpp:79-98,
+//             hip_kernels/dsv4_all_hip_kernels.hip:172-196 for the masked form)
+// gate and up may be the two halves of one packed [M, 2N] tensor: ldg/ldu are row
+// strides in elements.
+// ====================================================================================
+template <int VPT, int MAXT>
+__global__ void __launch_bounds__(MAXT) silu_mul_quant_vec_kernel(
+    const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
+    const int* __restrict__ mask, int8_t* __restrict__ q, float* __restrict__ s, int M, int N,
+    int64_t ldg, int64_t ldu) {
+    __shared__ float red[32];
+    const int V = N >> 3, T = blockDim.x, tid = threadIdx.x;
+    for (int row = blockIdx.x; row < M; row += gridDim.x) {
+        if (mask != nullptr && mask[row] == 0) continue;  // uniform over the block
+        const uint4* gr = reinterpret_cast<const uint4*>(g + (int64_t)row * ldg);
+        const uint4* ur = reinterpret_cast<const uint4*>(u + (int64_t)row * ldu);
+        uint4 gv[VPT], uv[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int idx = tid + i * T;
+            if (idx < V) {
+                gv[i] = ld_stream(gr + idx);
+                uv[i] = ld_stream(ur + idx);
+            } else {
+                gv[i] = make_uint4(0, 0, 0, 0);
+                uv[i] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        float h[VPT][8];
+        float am = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            float g8[8], u8[8];
+            unpack8(gv[i], g8);
+            unpack8(uv[i], u8);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                h[i][e] = silu_mul(g8[e], u8[e]);
+                am = fmaxf(am, fabsf(h[i][e]));
+            }
+        }
+        am = block_max(am, red);
+        float scale, inv;
+        scale_from_amax(am, scale, inv);
+        if (tid == 0) s[row] = scale;
+        uint2* qr = reinterpret_cast<uint2*>(q + (int64_t)row * N);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int idx = tid + i * T;
+            if (idx < V) qr[idx] = quant8_rn(h[i], inv);
+        }
+        __syncthreads();
+    }
+}
+
+__global__ void __launch_bounds__(256) silu_mul_quant_generic_kernel(
+    const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
+    const int* __restrict__ mask, int8_t* __restrict__ q, float* __restrict__ s, int M, int N,
+    int64_t ldg, int64_t ldu) {
+    __shared__ float red[32];
+    for (int row = blockIdx.x; row < M; row += gridDim.x) {
+        if (mask != nullptr && mask[row] == 0) continue;
+        const __nv_bfloat16* gr = g + (int64_t)row * ldg;
+        const __nv_bfloat16* ur = u + (int64_t)row * ldu;
+        float am = 0.0f;
+        for (int j = threadIdx.x; j < N; j += blockDim.x)
+            am = fmaxf(am, fabsf(silu_mul(__bfloat162float(gr[j]), __bfloat162float(ur[j]))));
+        am = block_max(am, red);
+        float scale, inv;
+        scale_from_amax(am, scale, inv);
+        if (threadIdx.x == 0) s[row] = scale;
+        int8_t* qr = q + (int64_t)row * N;
+        for (int j = threadIdx.x; j < N; j += blockDim.x)
+            qr[j] = (int8_t)quant_rn(silu_mul(__bfloat162float(gr[j]), __bfloat162float(ur[j])), inv);
+        __syncthreads();
+    }
+}
+
+// ====================================================================================
+// silu_and_mul -> bf16  (reference: hip_kernels/dsv4_native_ext.cpp:65-74)
+// ====================================================================================
+__global__ void __launch_bounds__(256) silu_mul_vec_kernel(const __nv_bfloat16* __restrict__ g,
+                                                           const __nv_bfloat16* __restrict__ u,
+                                                           __nv_bfloat16* __restrict__ out, int M,
+                                                           int N, int64_t ldg, int64_t ldu) {
+    const int V = N >> 3;
+    const int64_t total = (int64_t)M * V;
+    for (int64_t f = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; f < total;
+         f += (int64_t)gridDim.x * blockDim.x) {
+        const int row = (int)(f / V), idx = (int)(f % V);
+        const uint4 gv = ld_stream(reinterpret_cast<const uint4*>(g + (int64_t)row * ldg) + idx);
+        const uint4 uv = ld_stream(reinterpret_cast<const uint4*>(u + (int64_t)row * ldu) + idx);
+        float g8[8], u8[8], h[8];
+        unpack8(gv, g8);
+        unpack8(uv, u8);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) h[e] = silu_mul(g8[e], u8[e]);
+        uint4 o;
+        o.x = pack_bf16x2_rn(h[0], h[1]);
+        o.y = pack_bf16x2_rn(h[2], h[3]);
+        o.z = pack_bf16x2_rn(h[4], h[5]);
+        o.w = pack_bf16x2_rn(h[6], h[7]);
+        reinterpret_cast<uint4*>(out + (int64_t)row * N)[idx] = o;
+    }
+}
+
+__global__ void __launch_bounds__(256) silu_mul_generic_kernel(const __nv_bfloat16* __restrict__ g,
+                                                               const __nv_bfloat16* __restrict__ u,
+                                                               __nv_bfloat16* __restrict__ out,
+                                                               int M, int N, int64_t ldg,
+                                                               int64_t ldu) {
+    const int64_t total = (int64_t)M * N;
+    for (int64_t f = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; f < total;
+         f += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = f / N, j = f % N;
+        out[f] = __float2bfloat16_rn(
+            silu_mul(__bfloat162float(g[row * ldg + j]), __bfloat162float(u[row * ldu + j])));
+    }
+}
+
+// ====================================================================================
+// host-side launchers
+// ====================================================================================
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+static inline int round_up32(int v) { return (v + 31) & ~31; }
+static inline int grid_rows(int M) { return M; }
+
+int ptq(const void* x, void* q, void* s, int M, int K, int64_t ldx, cudaStream_t st) {
+    if (M == 0 || K == 0) return 0;
+    auto xp = static_cast<const __nv_bfloat16*>(x);
+    auto qp = static_cast<int8_t*>(q);
+    auto sp = static_cast<float*>(s);
+    const bool vec = (K % 8 == 0) && (ldx % 8 == 0) && aligned16(x) && ((reinterpret_cast<uintptr_t>(q) & 7) == 0);
+    const int V = K / 8;
+    if (vec && V <= 4 * 1024) {
+        if (V <= 1024) {  // one vector per thread up to 8192 columns
+            int T = round_up32(V);
+            if (V > 512) {
+                ptq_vec_kernel<2><<<grid_rows(M), round_up32((V + 1) / 2), 0, st>>>(xp, qp, sp, M, K, ldx);
+            } else {
+                ptq_vec_kernel<1><<<grid_rows(M), T < 64 ? 64 : T, 0, st>>>(xp, qp, sp, M, K, ldx);
+            }
+        } else if (V <= 2048) {
+            ptq_vec_kernel<2><<<grid_rows(M), round_up32((V + 1) / 2), 0, st>>>(xp, qp, sp, M, K, ldx);
+        } else {
+            ptq_vec_kernel<4><<<grid_rows(M), round_up32((V + 3) / 4), 0, st>>>(xp, qp, sp, M, K, ldx);
+        }
+    } else {
+        ptq_generic_kernel<<<grid_rows(M), 256, 0, st>>>(xp, qp, sp, M, K, ldx);
+    }
+    return check_launch("per_token_quant_int8");
+}
+
+int ptgq(const void* x, void* q, void* s, int M, int K, int gs, cudaStream_t st) {
+    if (M == 0 || K == 0) return 0;
+    if (gs <= 0) return fail(DSV4_ERR_ARG, "per_token_group_quant_int8: group_size must be positive");
+    const bool vec = (K % gs == 0) && (gs % 8 == 0) && aligned16(x) &&
+                     ((reinterpret_cast<uintptr_t>(q) & 7) == 0);
+    const int lpg = gs / 8;
+    const int64_t nvec = (int64_t)M * (K / 8);
+    auto xv = static_cast<const uint4*>(x);
+    auto qv = static_cast<uint2*>(q);
+    auto sp = static_cast<float*>(s);
+    const int64_t want = (nvec + 256 * 2 - 1) / (256 * 2);
+    const int grid = (int)(want < 1 ? 1 : (want > (1 << 20) ? (1 << 20) : want));
+    bool done = false;
+    if (vec) {
+        done = true;
+        switch (lpg) {
+            case 1: ptgq_vec_kernel<1, 2><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
+            case 2: ptgq_vec_kernel<2, 2><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
+            case 4: ptgq_vec_kernel<4, 2><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
+            case 8: ptgq_vec_kernel<8, 2><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
+            case 16: ptgq_vec_kernel<16, 2><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
+            case 32: ptgq_vec_kernel<32, 2><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
+            default: done = false;
+        }
+    }
+    if (!done) {
+        const int64_t groups = (int64_t)M * ((K + gs - 1) / gs);
+        const int64_t blocks = (groups + 7) / 8;
+        ptgq_generic_kernel<<<(int)(blocks > (1 << 20) ? (1 << 20) : blocks), 256, 0, st>>>(
+            static_cast<const __nv_bfloat16*>(x), static_cast<int8_t*>(q), sp, M, K, gs, K);
+    }
+    return check_launch("per_token_group_quant_int8");
+}
+
+int add_rmsnorm_quant(void* res, const void* x, const void* w, void* q, void* s, int M, int K,
+                      float eps, cudaStream_t st) {
+    if (M == 0 || K == 0) return 0;
+    auto rp = static_cast<__nv_bfloat16*>(res);
+    auto xp = static_cast<const __nv_bfloat16*>(x);
+    auto wp = static_cast<const __nv_bfloat16*>(w);
+    auto qp = static_cast<int8_t*>(q);
+    auto sp = static_cast<float*>(s);
+    const bool vec = (K % 8 == 0) && aligned16(res) && aligned16(x) && aligned16(w) &&
+                     ((reinterpret_cast<uintptr_t>(q) & 7) == 0);
+    const int V = K / 8;
+    if (vec && V <= 8 * kSumLanes) {
+        if (V <= kSumLanes)
+            add_rmsnorm_quant_vec_kernel<1><<<grid_rows(M), kSumLanes, 0, st>>>(rp, xp, wp, qp, sp, M, K, eps);
+        else if (V <= 2 * kSumLanes)
+            add_rmsnorm_quant_vec_kernel<2><<<grid_rows(M), kSumLanes, 0, st>>>(rp, xp, wp, qp, sp, M, K, eps);
+        else if (V <= 4 * kSumLanes)
+            add_rmsnorm_quant_vec_kernel<4><<<grid_rows(M), kSumLanes, 0, st>>>(rp, xp, wp, qp, sp, M, K, eps);
+        else
+            add_rmsnorm_quant_vec_kernel<8><<<grid_rows(M), kSumLanes, 0, st>>>(rp, xp, wp, qp, sp, M, K, eps);
+    } else {
+        add_rmsnorm_quant_generic_kernel<<<grid_rows(M), kSumLanes, 0, st>>>(rp, xp, wp, qp, sp, M, K, eps);
+    }
+    return check_launch("add_rmsnorm_quant");
+}
+
+int rmsnorm(void* x, int M, int K, float eps, cudaStream_t st) {
+    if (M == 0 || K == 0) return 0;
+    auto xp = static_cast<__nv_bfloat16*>(x);
+    const bool vec = (K % 8 == 0) && aligned16(x);
+    const int V = K / 8;
+    if (vec && V <= 8 * kSumLanes) {
+        if (V <= kSumLanes) rmsnorm_vec_kernel<1><<<grid_rows(M), kSumLanes, 0, st>>>(xp, M, K, eps);
+        else if (V <= 2 * kSumLanes) rmsnorm_vec_kernel<2><<<grid_rows(M), kSumLanes, 0, st>>>(xp, M, K, eps);
+        else if (V <= 4 * kSumLanes) rmsnorm_vec_kernel<4><<<grid_rows(M), kSumLanes, 0, st>>>(xp, M, K, eps);
+        else rmsnorm_vec_kernel<8><<<grid_rows(M), kSumLanes, 0, st>>>(xp, M, K, eps);
+    } else {
+        rmsnorm_generic_kernel<<<grid_rows(M), kSumLanes, 0, st>>>(xp, M, K, eps);
+    }
+    return check_launch("rmsnorm");
+}
+
+int silu_mul_quant(const void* g, const void* u, const int* mask, void* q, void* s, int M, int N,
+                   int64_t ldg, int64_t ldu, cudaStream_t st) {
+    if (M == 0 || N == 0) return 0;
+    auto gp = static_cast<const __nv_bfloat16*>(g);
+    auto up = static_cast<const __nv_bfloat16*>(u);
+    auto qp = static_cast<int8_t*>(q);
+    auto sp = static_cast<float*>(s);
+    const bool vec = (N % 8 == 0) && (ldg % 8 == 0) && (ldu % 8 == 0) && aligned16(g) &&
+                     aligned16(u) && ((reinterpret_cast<uintptr_t>(q) & 7) == 0);
+    const int V = N / 8;
+    if (vec && V <= 4096) {
+        if (V <= 256) {
+            const int T = round_up32(V) < 64 ? 64 : round_up32(V);
+            silu_mul_quant_vec_kernel<1, 256><<<grid_rows(M), T, 0, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
+        } else if (V <= 1024) {
+            silu_mul_quant_vec_kernel<2, 512><<<grid_rows(M), round_up32((V + 1) / 2), 0, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
+        } else if (V <= 3072) {
+            silu_mul_quant_vec_kernel<4, 768><<<grid_rows(M), round_up32((V + 3) / 4), 0, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
+        } else {
+            silu_mul_quant_vec_kernel<8, 512><<<grid_rows(M), round_up32((V + 7) / 8), 0, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
+        }
+    } else {
+        silu_mul_quant_generic_kernel<<<grid_rows(M), 256, 0, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
+    }
+    return check_launch("silu_mul_quant");
+}
+
+int silu_mul(const void* g, const void* u, void* out, int M, int N, int64_t ldg, int64_t ldu,
+             cudaStream_t st) {
+    if (M == 0 || N == 0) return 0;
+    auto gp = static_cast<const __nv_bfloat16*>(g);
+    auto up = static_cast<const __nv_bfloat16*>(u);
+    auto op = static_cast<__nv_bfloat16*>(out);
+    const bool vec = (N % 8 == 0) && (ldg % 8 == 0) && (ldu % 8 == 0) && aligned16(g) &&
+                     aligned16(u) && aligned16(out);
+    const int64_t work = vec ? (int64_t)M * (N / 8) : (int64_t)M * N;
+    int64_t blocks = (work + 255) / 256;
+    if (blocks > (1 << 20)) blocks = 1 << 20;
+    if (vec)
+        silu_mul_vec_kernel<<<(int)blocks, 256, 0, st>>>(gp, up, op, M, N, ldg, ldu);
+    else
+        silu_mul_generic_kernel<<<(int)blocks, 256, 0, st>>>(gp, up, op, M, N, ldg, ldu);
+    return check_launch("silu_and_mul");
+}
+
+}  // namespace w8a8

@@ -1,0 +1,371 @@
+// Python operator boundary: the pybind11 module `dsv4_native_ext`.
+//
+// It keeps the operator names, argument order, return shapes and the RuntimeError
+// behaviour of the reference module (hip_kernels/dsv4_native_ext.cpp:314-444): every op
+// exists as `name(...)` and as `name_stream(..., stream_ptr)` where stream_ptr is the raw
+// stream handle (torch.cuda.current_stream().cuda_stream).  Each wrapper only checks its
+// arguments, allocates the outputs with torch and forwards plain pointers to the C-ABI
+// (include/dsv4_w8a8.h); there is no CPU path: a non-CUDA tensor raises.
+//
+// Differences from the reference, all additive or stricter:
+//   * `name(...)` launches on torch's current stream rather than on stream 0;
+//   * dtype / device / shape / alignment are checked (the reference checks contiguity only);
+//   * silu ops accept row-strided 2-D views, so the halves of a packed gate_up work;
+//   * new names: w8a8_gemm (alias), w8a8_gemm_i32, scale_convert,
+//     per_token_group_quant_int8, silu_mul_masked_quant, grouped_gemm, moe_segments,
+//     gather_rows, device_status;
+//   * flash_mla_decode is not part of the W8A8 path and is not provided.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/dsv4_w8a8.h"
+
+namespace {
+
+using torch::Tensor;
+
+// `name(...)` variants pass this sentinel; it is resolved to torch's current stream on the
+// tensors' device after the argument checks and the device guard.
+constexpr int64_t kCurrentStream = INT64_MIN;
+inline int64_t current_stream_ptr() { return kCurrentStream; }
+inline dsv4_stream_t as_stream(int64_t stream_ptr) {
+    if (stream_ptr == kCurrentStream) return reinterpret_cast<dsv4_stream_t>(at::cuda::getCurrentCUDAStream().stream());
+    return reinterpret_cast<dsv4_stream_t>(stream_ptr);
+}
+
+void check_status(int rc) {
+    TORCH_CHECK(rc == 0, "dsv4_native_ext: ", dsv4_last_error(), " (status ", rc, ")");
+}
+
+void check_cuda(const Tensor& t, const char* name, c10::ScalarType dtype) {
+    TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor (this extension has no CPU path)");
+    TORCH_CHECK(t.scalar_type() == dtype, name, " must have dtype ", dtype, ", got ", t.scalar_type());
+}
+
+void check_same_device(const Tensor& a, const Tensor& b, const char* what) {
+    TORCH_CHECK(a.device() == b.device(), what, ": tensors are on different devices");
+}
+
+int to_int(int64_t v, const char* what) {
+    TORCH_CHECK(v >= 0 && v <= INT32_MAX, what, " does not fit in int32: ", v);
+    return static_cast<int>(v);
+}
+
+struct Rows {
+    int M, N;
+};
+Rows rows_of(const Tensor& x) {
+    TORCH_CHECK(x.dim() >= 1, "expected at least one dimension");
+    const int64_t n = x.size(-1);
+    const int64_t m = n == 0 ? 0 : x.numel() / n;
+    return {to_int(m, "rows"), to_int(n, "row length")};
+}
+
+// ---- per_token_quant_int8 (reference wrapper :314-324) ----------------------------
+std::vector<Tensor> per_token_quant_int8_stream(Tensor x, int64_t stream_ptr) {
+    TORCH_CHECK(x.is_contiguous());
+    check_cuda(x, "x", torch::kBFloat16);
+    c10::cuda::CUDAGuard guard(x.device());
+    const Rows r = rows_of(x);
+    auto q = torch::empty_like(x, x.options().dtype(torch::kInt8));
+    auto s = torch::empty({r.M}, x.options().dtype(torch::kFloat32));
+    check_status(launch_ptq(x.data_ptr(), q.data_ptr(), s.data_ptr(), r.M, r.N, as_stream(stream_ptr)));
+    return {q, s.unsqueeze(-1)};
+}
+
+// ---- per_token_group_quant_int8 (launcher dsv4_all_hip_kernels.hip:346-350) -------
+std::vector<Tensor> per_token_group_quant_int8_stream(Tensor x, int64_t group_size, int64_t stream_ptr) {
+    TORCH_CHECK(x.is_contiguous());
+    check_cuda(x, "x", torch::kBFloat16);
+    TORCH_CHECK(group_size > 0, "group_size must be positive");
+    c10::cuda::CUDAGuard guard(x.device());
+    const Rows r = rows_of(x);
+    const int64_t groups = (r.N + group_size - 1) / group_size;
+    auto q = torch::empty_like(x, x.options().dtype(torch::kInt8));
+    auto s = torch::empty({r.M, groups}, x.options().dtype(torch::kFloat32));
+    check_status(launch_ptgq(x.data_ptr(), q.data_ptr(), s.data_ptr(), r.M, r.N, to_int(group_size, "group_size"),
+                             as_stream(stream_ptr)));
+    return {q, s};
+}
+
+// ---- rmsnorm (reference wrapper :326-334): in place, returns x --------------------
+Tensor rmsnorm_stream(Tensor x, double eps, int64_t stream_ptr) {
+    TORCH_CHECK(x.is_contiguous());
+    check_cuda(x, "x", torch::kBFloat16);
+    TORCH_CHECK(x.dim() == 2, "rmsnorm expects a 2-D tensor");
+    c10::cuda::CUDAGuard guard(x.device());
+    check_status(launch_rmsnorm(x.data_ptr(), to_int(x.size(0), "M"), to_int(x.size(1), "N"), (float)eps,
+                                as_stream(stream_ptr)));
+    return x;
+}
+
+struct GateUp {
+    int M, N;
+    int64_t ldg, ldu;
+};
+GateUp check_gate_up(const Tensor& gate, const Tensor& up) {
+    check_cuda(gate, "gate", torch::kBFloat16);
+    check_cuda(up, "up", torch::kBFloat16);
+    check_same_device(gate, up, "gate/up");
+    TORCH_CHECK(gate.dim() == 2 && up.dim() == 2, "gate and up must be 2-D");
+    TORCH_CHECK(gate.sizes() == up.sizes(), "gate and up must have the same shape");
+    // the reference requires gate.is_contiguous(); a unit inner stride is enough here
+    TORCH_CHECK(gate.size(1) == 0 || (gate.stride(1) == 1 && up.stride(1) == 1),
+                "gate and up must have unit stride in the last dimension");
+    return {to_int(gate.size(0), "M"), to_int(gate.size(1), "N"), gate.stride(0), up.stride(0)};
+}
+
+// ---- silu_and_mul (reference wrapper :336-346) -------------------------------------
+Tensor silu_and_mul_stream(Tensor gate, Tensor up, int64_t stream_ptr) {
+    const GateUp g = check_gate_up(gate, up);
+    c10::cuda::CUDAGuard guard(gate.device());
+    auto out = torch::empty({g.M, g.N}, gate.options());
+    if (g.ldg == g.N && g.ldu == g.N) {
+        check_status(launch_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(), g.M, g.N, as_stream(stream_ptr)));
+    } else {
+        auto gc = gate.contiguous(), uc = up.contiguous();
+        check_status(launch_silu_mul(gc.data_ptr(), uc.data_ptr(), out.data_ptr(), g.M, g.N, as_stream(stream_ptr)));
+    }
+    return out;
+}
+
+// ---- silu_mul_quant (reference wrapper :348-359) -----------------------------------
+std::vector<Tensor> silu_mul_quant_stream(Tensor gate, Tensor up, int64_t stream_ptr) {
+    const GateUp g = check_gate_up(gate, up);
+    c10::cuda::CUDAGuard guard(gate.device());
+    auto q = torch::empty({g.M, g.N}, gate.options().dtype(torch::kInt8));
+    auto s = torch::empty({g.M}, gate.options().dtype(torch::kFloat32));
+    check_status(launch_silu_mul_quant_strided(gate.data_ptr(), g.ldg, up.data_ptr(), g.ldu, nullptr, q.data_ptr(),
+                                               s.data_ptr(), g.M, g.N, as_stream(stream_ptr)));
+    return {q, s.unsqueeze(-1)};
+}
+
+// masked form (launcher dsv4_all_hip_kernels.hip:362-366): rows with mask == 0 are skipped;
+// their q and s entries are returned as zero.
+std::vector<Tensor> silu_mul_masked_quant_stream(Tensor gate, Tensor up, Tensor mask, int64_t stream_ptr) {
+    const GateUp g = check_gate_up(gate, up);
+    check_cuda(mask, "mask", torch::kInt32);
+    TORCH_CHECK(mask.is_contiguous() && mask.numel() == g.M, "mask must be a contiguous int32 tensor of M entries");
+    c10::cuda::CUDAGuard guard(gate.device());
+    auto q = torch::zeros({g.M, g.N}, gate.options().dtype(torch::kInt8));
+    auto s = torch::zeros({g.M}, gate.options().dtype(torch::kFloat32));
+    check_status(launch_silu_mul_quant_strided(gate.data_ptr(), g.ldg, up.data_ptr(), g.ldu,
+                                               static_cast<const int*>(mask.data_ptr()), q.data_ptr(), s.data_ptr(),
+                                               g.M, g.N, as_stream(stream_ptr)));
+    return {q, s.unsqueeze(-1)};
+}
+
+// ---- add_rmsnorm_quant (reference wrapper :361-373): res is overwritten with res+x --
+std::vector<Tensor> add_rmsnorm_quant_stream(Tensor res, Tensor x, Tensor w, double eps, int64_t stream_ptr) {
+    TORCH_CHECK(res.is_contiguous());
+    check_cuda(res, "res", torch::kBFloat16);
+    check_cuda(x, "x", torch::kBFloat16);
+    check_cuda(w, "w", torch::kBFloat16);
+    check_same_device(res, x, "res/x");
+    check_same_device(res, w, "res/w");
+    TORCH_CHECK(x.dim() == 2, "x must be 2-D");
+    TORCH_CHECK(x.is_contiguous() && w.is_contiguous(), "x and w must be contiguous");
+    TORCH_CHECK(res.sizes() == x.sizes(), "res and x must have the same shape");
+    TORCH_CHECK(w.numel() == x.size(1), "w must have N entries");
+    c10::cuda::CUDAGuard guard(x.device());
+    const int M = to_int(x.size(0), "M"), N = to_int(x.size(1), "N");
+    auto q = torch::empty_like(x, x.options().dtype(torch::kInt8));
+    auto s = torch::empty({M}, x.options().dtype(torch::kFloat32));
+    check_status(launch_add_rmsnorm_quant(res.data_ptr(), x.data_ptr(), w.data_ptr(), q.data_ptr(), s.data_ptr(), M,
+                                          N, (float)eps, as_stream(stream_ptr)));
+    return {q, s.unsqueeze(-1)};
+}
+
+// ---- w8a8_scaled_gemm (reference wrapper :375-387) ---------------------------------
+struct GemmShape {
+    int M, N, K;
+};
+GemmShape check_gemm_operands(const Tensor& A, const Tensor& B) {
+    check_cuda(A, "A", torch::kInt8);
+    check_cuda(B, "B", torch::kInt8);
+    check_same_device(A, B, "A/B");
+    TORCH_CHECK(A.dim() == 2 && B.dim() == 2, "A must be [M,K] and B [N,K]");
+    TORCH_CHECK(A.is_contiguous() && B.is_contiguous(), "A and B must be contiguous");
+    TORCH_CHECK(A.size(1) == B.size(1), "A and B disagree on K: ", A.size(1), " vs ", B.size(1));
+    return {to_int(A.size(0), "M"), to_int(B.size(0), "N"), to_int(A.size(1), "K")};
+}
+Tensor flat_scale(const Tensor& s, int64_t n, const char* name) {
+    check_cuda(s, name, torch::kFloat32);
+    TORCH_CHECK(s.numel() == n, name, " must have ", n, " entries, got ", s.numel());
+    return s.contiguous();
+}
+
+Tensor w8a8_scaled_gemm_stream(Tensor A, Tensor B, Tensor sa, Tensor sb, int64_t stream_ptr) {
+    const GemmShape g = check_gemm_operands(A, B);
+    auto sa_c = flat_scale(sa, g.M, "sa");
+    auto sb_c = flat_scale(sb, g.N, "sb");
+    c10::cuda::CUDAGuard guard(A.device());
+    auto C = torch::empty({g.M, g.N}, A.options().dtype(torch::kBFloat16));
+    check_status(launch_w8a8_gemm(A.data_ptr(), B.data_ptr(), sa_c.data_ptr(), sb_c.data_ptr(), C.data_ptr(), g.M,
+                                  g.N, g.K, as_stream(stream_ptr)));
+    return C;
+}
+
+Tensor w8a8_gemm_i32_stream(Tensor A, Tensor B, int64_t stream_ptr) {
+    const GemmShape g = check_gemm_operands(A, B);
+    c10::cuda::CUDAGuard guard(A.device());
+    auto C = torch::empty({g.M, g.N}, A.options().dtype(torch::kInt32));
+    check_status(launch_w8a8_gemm_i32(A.data_ptr(), B.data_ptr(), C.data_ptr(), g.M, g.N, g.K, as_stream(stream_ptr)));
+    return C;
+}
+
+Tensor scale_convert_stream(Tensor acc, Tensor sa, Tensor sb, int64_t stream_ptr) {
+    check_cuda(acc, "acc", torch::kInt32);
+    TORCH_CHECK(acc.dim() == 2 && acc.is_contiguous(), "acc must be a contiguous [M,N] tensor");
+    auto sa_c = flat_scale(sa, acc.size(0), "sa");
+    auto sb_c = flat_scale(sb, acc.size(1), "sb");
+    c10::cuda::CUDAGuard guard(acc.device());
+    auto out = torch::empty_like(acc, acc.options().dtype(torch::kBFloat16));
+    check_status(launch_scale_convert(acc.data_ptr(), sa_c.data_ptr(), sb_c.data_ptr(), out.data_ptr(),
+                                      to_int(acc.size(0), "M"), to_int(acc.size(1), "N"), as_stream(stream_ptr)));
+    return out;
+}
+
+// ---- grouped_gemm ------------------------------------------------------------------
+Tensor grouped_gemm_stream(Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor expert_offsets, int64_t stream_ptr) {
+    check_cuda(A, "A", torch::kInt8);
+    check_cuda(W, "W", torch::kInt8);
+    check_cuda(sa, "sa", torch::kFloat32);
+    check_cuda(sw, "sw", torch::kFloat32);
+    check_cuda(expert_offsets, "expert_offsets", torch::kInt32);
+    check_same_device(A, W, "A/W");
+    TORCH_CHECK(A.dim() == 2 && W.dim() == 3, "A must be [R,K] and W [E,N,K]");
+    TORCH_CHECK(A.is_contiguous() && W.is_contiguous() && sw.is_contiguous() && expert_offsets.is_contiguous(),
+                "A, W, sw and expert_offsets must be contiguous");
+    const int R = to_int(A.size(0), "R"), K = to_int(A.size(1), "K");
+    const int E = to_int(W.size(0), "E"), N = to_int(W.size(1), "N");
+    TORCH_CHECK(W.size(2) == K, "A and W disagree on K");
+    TORCH_CHECK(sw.numel() == (int64_t)E * N, "sw must be [E,N]");
+    TORCH_CHECK(expert_offsets.numel() == E + 1, "expert_offsets must have E+1 entries");
+    auto sa_c = sa.contiguous();
+    int groups = 1;
+    if (sa_c.numel() != R) {
+        TORCH_CHECK(K % 128 == 0 && sa_c.numel() == (int64_t)R * (K / 128),
+                    "sa must have R entries (per token) or be [R, K/128] (per 128-wide group)");
+        groups = K / 128;
+    }
+    c10::cuda::CUDAGuard guard(A.device());
+    auto C = torch::empty({R, N}, A.options().dtype(torch::kBFloat16));
+    check_status(launch_grouped_gemm(A.data_ptr(), W.data_ptr(), sa_c.data_ptr(), sw.data_ptr(),
+                                     static_cast<const int*>(expert_offsets.data_ptr()), C.data_ptr(), R, E, N, K,
+                                     groups, as_stream(stream_ptr)));
+    return C;
+}
+
+std::vector<Tensor> moe_segments_stream(Tensor topk_ids, int64_t num_experts, int64_t stream_ptr) {
+    check_cuda(topk_ids, "topk_ids", torch::kInt32);
+    TORCH_CHECK(topk_ids.dim() == 2 && topk_ids.is_contiguous(), "topk_ids must be a contiguous [T,topk] tensor");
+    c10::cuda::CUDAGuard guard(topk_ids.device());
+    const int T = to_int(topk_ids.size(0), "T"), topk = to_int(topk_ids.size(1), "topk");
+    auto opt = topk_ids.options();
+    auto offsets = torch::empty({num_experts + 1}, opt);
+    auto src_row = torch::empty({(int64_t)T * topk}, opt);
+    auto dst_slot = torch::empty({(int64_t)T * topk}, opt);
+    if (T == 0) {
+        offsets.zero_();
+        return {offsets, src_row, dst_slot};
+    }
+    check_status(launch_moe_segments(static_cast<const int*>(topk_ids.data_ptr()), T, topk,
+                                     to_int(num_experts, "num_experts"), static_cast<int*>(offsets.data_ptr()),
+                                     static_cast<int*>(src_row.data_ptr()), static_cast<int*>(dst_slot.data_ptr()),
+                                     as_stream(stream_ptr)));
+    return {offsets, src_row, dst_slot};
+}
+
+// rows of `src` ([T, row]) gathered by src_row; `scales` ([T, spr] or [T,1]) optional
+std::vector<Tensor> gather_rows_stream(Tensor src, Tensor src_row, c10::optional<Tensor> scales, int64_t stream_ptr) {
+    TORCH_CHECK(src.is_cuda() && src.dim() == 2 && src.is_contiguous(), "src must be a contiguous 2-D CUDA tensor");
+    check_cuda(src_row, "src_row", torch::kInt32);
+    TORCH_CHECK(src_row.is_contiguous(), "src_row must be contiguous");
+    c10::cuda::CUDAGuard guard(src.device());
+    const int R = to_int(src_row.numel(), "R");
+    const int64_t row_bytes = src.size(1) * src.element_size();
+    auto dst = torch::empty({R, src.size(1)}, src.options());
+    Tensor dscale;
+    const float* sp = nullptr;
+    float* dp = nullptr;
+    int spr = 0;
+    Tensor sc;
+    if (scales.has_value()) {
+        sc = scales->contiguous();
+        check_cuda(sc, "scales", torch::kFloat32);
+        TORCH_CHECK(sc.dim() == 2 && sc.size(0) == src.size(0), "scales must be [T, n]");
+        spr = to_int(sc.size(1), "scales per row");
+        dscale = torch::empty({R, sc.size(1)}, sc.options());
+        sp = static_cast<const float*>(sc.data_ptr());
+        dp = static_cast<float*>(dscale.data_ptr());
+    }
+    check_status(launch_gather_rows(src.data_ptr(), static_cast<const int*>(src_row.data_ptr()), dst.data_ptr(), R,
+                                    to_int(row_bytes, "row bytes"), sp, dp, spr, as_stream(stream_ptr)));
+    if (scales.has_value()) return {dst, dscale};
+    return {dst};
+}
+
+int64_t device_status() {
+    int v = 0;
+    check_status(dsv4_device_status(as_stream(current_stream_ptr()), &v));
+    return v;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.doc() = "B200 (sm_100a) W8A8 linear path behind the dsv4_native_ext operator names";
+    // the reference's names (hip_kernels/dsv4_native_ext.cpp:429-444)
+    m.def("per_token_quant_int8", [](Tensor x) { return per_token_quant_int8_stream(x, current_stream_ptr()); });
+    m.def("per_token_quant_int8_stream", &per_token_quant_int8_stream);
+    m.def("rmsnorm", [](Tensor x, double eps) { return rmsnorm_stream(x, eps, current_stream_ptr()); });
+    m.def("rmsnorm_stream", &rmsnorm_stream);
+    m.def("silu_and_mul", [](Tensor g, Tensor u) { return silu_and_mul_stream(g, u, current_stream_ptr()); });
+    m.def("silu_and_mul_stream", &silu_and_mul_stream);
+    m.def("silu_mul_quant", [](Tensor g, Tensor u) { return silu_mul_quant_stream(g, u, current_stream_ptr()); });
+    m.def("silu_mul_quant_stream", &silu_mul_quant_stream);
+    m.def("add_rmsnorm_quant", [](Tensor res, Tensor x, Tensor w, double eps) {
+        return add_rmsnorm_quant_stream(res, x, w, eps, current_stream_ptr());
+    });
+    m.def("add_rmsnorm_quant_stream", &add_rmsnorm_quant_stream);
+    m.def("w8a8_scaled_gemm", [](Tensor A, Tensor B, Tensor sa, Tensor sb) {
+        return w8a8_scaled_gemm_stream(A, B, sa, sb, current_stream_ptr());
+    });
+    m.def("w8a8_scaled_gemm_stream", &w8a8_scaled_gemm_stream);
+    // additions
+    m.def("w8a8_gemm", [](Tensor A, Tensor B, Tensor sa, Tensor sb) {
+        return w8a8_scaled_gemm_stream(A, B, sa, sb, current_stream_ptr());
+    });
+    m.def("w8a8_gemm_stream", &w8a8_scaled_gemm_stream);
+    m.def("w8a8_gemm_i32", [](Tensor A, Tensor B) { return w8a8_gemm_i32_stream(A, B, current_stream_ptr()); });
+    m.def("w8a8_gemm_i32_stream", &w8a8_gemm_i32_stream);
+    m.def("scale_convert", [](Tensor acc, Tensor sa, Tensor sb) {
+        return scale_convert_stream(acc, sa, sb, current_stream_ptr());
+    });
+    m.def("scale_convert_stream", &scale_convert_stream);
+    m.def("per_token_group_quant_int8", [](Tensor x, int64_t gs) {
+        return per_token_group_quant_int8_stream(x, gs, current_stream_ptr());
+    }, py::arg("x"), py::arg("group_size") = 128);
+    m.def("per_token_group_quant_int8_stream", &per_token_group_quant_int8_stream);
+    m.def("silu_mul_masked_quant", [](Tensor g, Tensor u, Tensor mask) {
+        return silu_mul_masked_quant_stream(g, u, mask, current_stream_ptr());
+    });
+    m.def("silu_mul_masked_quant_stream", &silu_mul_masked_quant_stream);
+    m.def("grouped_gemm", [](Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor off) {
+        return grouped_gemm_stream(A, W, sa, sw, off, current_stream_ptr());
+    });
+    m.def("grouped_gemm_stream", &grouped_gemm_stream);
+    m.def("moe_segments", [](Tensor ids, int64_t E) { return moe_segments_stream(ids, E, current_stream_ptr()); });
+    m.def("moe_segments_stream", &moe_segments_stream);
+    m.def("gather_rows", [](Tensor src, Tensor src_row, c10::optional<Tensor> scales) {
+        return gather_rows_stream(src, src_row, scales, current_stream_ptr());
+    }, py::arg("src"), py::arg("src_row"), py::arg("scales") = py::none());
+    m.def("gather_rows_stream", &gather_rows_stream);
+    m.def("device_status", &device_status);
+    m.def("abi_version", [] { return dsv4_abi_version(); });
+}

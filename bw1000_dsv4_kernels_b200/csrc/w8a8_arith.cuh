@@ -1,0 +1,128 @@
+// Scalar arithmetic of the W8A8 activation-quant chain, device side.
+//
+// Every floating-point step that decides an int8 code or an fp32 scale is written
+// here with an explicitly rounded intrinsic (__fmul_rn, __fadd_rn, __fmaf_rn,
+// __fdiv_rn, __fsqrt_rn) so that the compiler can neither contract a multiply and an
+// add into an FMA nor substitute an approximate reciprocal / rsqrt / exp.  The same
+// sequence of IEEE-754 binary32 operations is restated for the CPU in the test
+// oracle; the two agree bit for bit because each step is a correctly rounded
+// operation on both sides.
+//
+// Reference arithmetic this follows (hip_kernels/dsv4_native_ext.cpp):
+//   quantiser        :24-40   am=max(amax,1e-10); s=am/127; inv=127/am; q=rint(x*inv)
+//   add + rmsnorm    :103-132 a=res+x; rrms=rsqrt(sum(a*a)/N+eps); y=(a*rrms)*w
+//   silu * up        :79-98   h=((1/(1+exp(-g)))*g)*u
+//   group quantiser  hip_kernels/dsv4_all_hip_kernels.hip:49-86  q=trunc(clamp(x/s))
+// Two deliberate differences, both needed for a reproducible result:
+//   * rsqrt is computed as 1/sqrt with correctly rounded sqrt and divide;
+//   * exp is the fixed polynomial below, not a vendor libm routine.
+#pragma once
+#include <cstdint>
+#include <cuda_bf16.h>
+
+namespace w8a8 {
+
+constexpr float kAmaxFloor = 1e-10f;
+
+// ---- bf16 <-> f32 -----------------------------------------------------------------
+// A 32-bit word holds two bf16 values; element 0 is the low half.
+__device__ __forceinline__ float bf16lo_to_f32(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi_to_f32(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// Round-to-nearest-even f32 -> bf16, two values packed (lo = a, hi = b).
+__device__ __forceinline__ uint32_t pack_bf16x2_rn(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// ---- quantiser --------------------------------------------------------------------
+// scale and inverse scale from a row (or group) absolute maximum
+__device__ __forceinline__ void scale_from_amax(float amax, float& scale, float& inv) {
+    float am = fmaxf(amax, kAmaxFloor);
+    scale = __fdiv_rn(am, 127.0f);
+    inv = __fdiv_rn(127.0f, am);
+}
+
+// round-half-even(x*inv), clamped to [-128,127].  cvt.rni.s32 is rintf followed by an
+// exact conversion; |x*inv| <= 127*(1+2^-23) for finite inputs so the clamp never
+// changes a value that came from the same row's amax, but it is kept for safety.
+__device__ __forceinline__ int quant_rn(float x, float inv) {
+    int q = __float2int_rn(__fmul_rn(x, inv));
+    return max(-128, min(127, q));
+}
+
+// group quantiser: true division by the stored scale, clamp, truncate toward zero
+__device__ __forceinline__ int quant_trunc_div(float x, float scale) {
+    float t = __fdiv_rn(x, scale);
+    t = fmaxf(-128.0f, fminf(127.0f, t));
+    return __float2int_rz(t);
+}
+
+__device__ __forceinline__ uint32_t pack_i8x4(int a, int b, int c, int d) {
+    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) |
+           ((uint32_t)(d & 0xff) << 24);
+}
+
+// ---- exp / sigmoid ----------------------------------------------------------------
+// exp_fixed(x) for x clamped to [-87, 87]:
+//   z = fma(x, log2e, 1.5*2^23)        (round x*log2e to an integer n in the low bits)
+//   n = z - 1.5*2^23
+//   r = fma(n, -ln2_hi, x); r = fma(n, -ln2_lo, r)
+//   p = 1 + r*(1 + r*(c2 + r*(c3 + r*(c4 + r*(c5 + r*c6)))))   (Horner, all fma)
+//   result = p * 2^n   (added to the exponent field; p*2^n stays a normal number)
+// Maximum observed error against a double-precision exp: 2.6 ulp of the result.
+constexpr float kExpClamp = 87.0f;
+constexpr float kLog2e = 1.44269502162933349609375f;        // 0x3FB8AA3B
+constexpr float kRoundMagic = 12582912.0f;                  // 1.5 * 2^23
+constexpr float kLn2Hi = 0.693145751953125f;                // 0x3F317200
+constexpr float kLn2Lo = 1.428606765330187045e-06f;         // 0x35BFBE8E
+constexpr float kExpC2 = 0.5f;
+constexpr float kExpC3 = 0.16666667163372039794921875f;     // 0x3E2AAAAB
+constexpr float kExpC4 = 0.0416666679084300994873046875f;   // 0x3D2AAAAB
+constexpr float kExpC5 = 0.008333333767950534820556640625f; // 0x3C088889
+constexpr float kExpC6 = 0.001388888922519981861114501953125f;  // 0x3AB60B61
+
+__device__ __forceinline__ float exp_fixed(float x) {
+    x = fminf(fmaxf(x, -kExpClamp), kExpClamp);
+    float z = __fmaf_rn(x, kLog2e, kRoundMagic);
+    float n = __fadd_rn(z, -kRoundMagic);
+    float r = __fmaf_rn(n, -kLn2Hi, x);
+    r = __fmaf_rn(n, -kLn2Lo, r);
+    float p = __fmaf_rn(r, kExpC6, kExpC5);
+    p = __fmaf_rn(r, p, kExpC4);
+    p = __fmaf_rn(r, p, kExpC3);
+    p = __fmaf_rn(r, p, kExpC2);
+    p = __fmaf_rn(r, p, 1.0f);
+    p = __fmaf_rn(r, p, 1.0f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(z) << 23));
+}
+
+// h = ((1/(1+exp(-g))) * g) * u, each step rounded to f32
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    float e = exp_fixed(-g);
+    float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, e));
+    return __fmul_rn(__fmul_rn(sig, g), u);
+}
+
+// rrms = 1 / sqrt(sumsq / n + eps)
+__device__ __forceinline__ float rrms_from_sumsq(float sumsq, int n, float eps) {
+    float mean = __fdiv_rn(sumsq, (float)n);
+    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+}
+
+// ---- reductions -------------------------------------------------------------------
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// xor butterfly, offsets 16,8,4,2,1: after it every lane holds the same sum, and the
+// association order is fixed (the oracle applies the same tree to 32 lane partials).
+__device__ __forceinline__ float warp_sum_butterfly(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+}  // namespace w8a8

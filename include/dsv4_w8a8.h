@@ -1,0 +1,156 @@
+/* C-ABI of the B200 (sm_100a) W8A8 linear path.
+ *
+ * This is the boundary a host program binds instead of the reference's HIP launchers.
+ * Every entry point takes plain device pointers and sizes, launches asynchronously on
+ * the given CUDA stream (0 = the legacy default stream), never synchronises the host
+ * and never allocates device memory.  All of them return an int status: 0 on success,
+ * one of the DSV4_ERR_* codes otherwise; dsv4_last_error() then gives a message for
+ * the calling thread.  (The reference launchers return void and report nothing.)
+ *
+ * Layouts: activations bf16 row-major; int8 codes row-major with the shape of the
+ * activation; scales fp32.  "M" is rows (tokens), "N" the row length of the
+ * quantisers (the reference's naming) and the output width of the GEMMs.
+ *
+ * Citations are file:line in the reference project (hip_kernels/...).
+ */
+#ifndef DSV4_W8A8_H
+#define DSV4_W8A8_H
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define DSV4_API __attribute__((visibility("default")))
+#else
+#define DSV4_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* cudaStream_t without pulling in the CUDA headers */
+typedef struct CUstream_st* dsv4_stream_t;
+
+enum {
+    DSV4_OK = 0,
+    DSV4_ERR_ARG = 1,         /* null pointer, negative size, unsupported stride/alignment */
+    DSV4_ERR_LAUNCH = 2,      /* the CUDA runtime rejected the launch */
+    DSV4_ERR_DRIVER = 3,      /* tensor-map creation failed / driver entry point missing */
+    DSV4_ERR_DEVICE_WAIT = 4  /* a bounded device-side wait gave up (see dsv4_device_status) */
+};
+
+#define DSV4_ABI_VERSION 1
+DSV4_API int dsv4_abi_version(void);
+
+/* Message for the last non-zero status returned on this thread ("" if none). */
+DSV4_API const char* dsv4_last_error(void);
+
+/* Synchronises `stream`, then reads and clears the current device's sticky status word
+ * that the GEMM kernels set when one of their bounded waits ran out (0 = none).
+ * Intended for tests and post-mortems; the launch path never calls it. */
+DSV4_API int dsv4_device_status(dsv4_stream_t stream, int* status_out);
+
+/* ---- activation quantisers ------------------------------------------------------ */
+
+/* per_token_quant_int8.  x bf16 [M,N] contiguous -> q int8 [M,N], s fp32 [M].
+ * Replaces launch_ptq, dsv4_all_hip_kernels.hip:343-345 (kernel :27-43). */
+DSV4_API int launch_ptq(const void* x, void* q, void* s, int M, int N, dsv4_stream_t stream);
+
+/* Same, with a row stride for x in elements (x may be a column slice of a wider tensor). */
+DSV4_API int launch_ptq_strided(const void* x, int64_t ldx, void* q, void* s, int M, int N,
+                       dsv4_stream_t stream);
+
+/* per_token_group_quant_int8.  x bf16 [M,N] contiguous -> q int8 [M,N],
+ * s fp32 [M, ceil(N/gs)] row-major.  q = trunc(clamp(x / s, -128, 127)).
+ * Replaces launch_ptgq, dsv4_all_hip_kernels.hip:346-350 (kernel :49-86). */
+DSV4_API int launch_ptgq(const void* x, void* q, void* s, int M, int N, int gs, dsv4_stream_t stream);
+
+/* add_rmsnorm_quant.  res <- res + x (bf16, in place); y = rmsnorm(res + x) * w;
+ * q,s = per-token quantisation of y.  res,x bf16 [M,N]; w bf16 [N].
+ * Replaces launch_add_rmsnorm_quant exported by libdsv4_ops_hip.so
+ * (kernel dsv4_native_ext.cpp:103-132). */
+DSV4_API int launch_add_rmsnorm_quant(void* res, const void* x, const void* w, void* q, void* s, int M,
+                             int N, float eps, dsv4_stream_t stream);
+
+/* silu_mul_quant.  h = silu(g) * u in fp32, then per-token quantisation.
+ * Replaces launch_silu_mul_quant exported by libdsv4_ops_hip.so
+ * (kernel dsv4_native_ext.cpp:79-98). */
+DSV4_API int launch_silu_mul_quant(const void* g, const void* u, void* q, void* s, int M, int N,
+                          dsv4_stream_t stream);
+
+/* Same with a row mask: rows whose mask[row] == 0 are skipped (q and s untouched).
+ * Replaces launch_silu_mul_masked_quant, dsv4_all_hip_kernels.hip:362-366. */
+DSV4_API int launch_silu_mul_masked_quant(const void* g, const void* u, const int* mask, void* q, void* s,
+                                 int M, int N, dsv4_stream_t stream);
+
+/* Same with row strides (elements) so that g and u can be the halves of one packed
+ * [M, 2N] gate_up tensor; mask may be null. */
+DSV4_API int launch_silu_mul_quant_strided(const void* g, int64_t ldg, const void* u, int64_t ldu,
+                                  const int* mask, void* q, void* s, int M, int N,
+                                  dsv4_stream_t stream);
+
+/* ---- unfused neighbours --------------------------------------------------------- */
+
+/* x <- x * rsqrt(mean(x^2) + eps), in place, no gamma.
+ * Replaces launch_rmsnorm (libdsv4_ops_hip.so) / launch_rmsnorm_self,
+ * dsv4_all_hip_kernels.hip:351-353. */
+DSV4_API int launch_rmsnorm(void* x, int M, int N, float eps, dsv4_stream_t stream);
+DSV4_API int launch_rmsnorm_self(void* x, int M, int N, float eps, dsv4_stream_t stream);
+
+/* out = bf16(silu(g) * u).  Replaces launch_silu_mul, dsv4_all_hip_kernels.hip:359-361. */
+DSV4_API int launch_silu_mul(const void* g, const void* u, void* out, int M, int N, dsv4_stream_t stream);
+
+/* ---- int8 GEMM ------------------------------------------------------------------ */
+
+/* C[m,n] = bf16((float(sum_k A[m,k]*B[n,k]) * sa[m]) * sb[n]).
+ * A int8 [M,K], B int8 [N,K] (both K contiguous), sa fp32 [M], sb fp32 [N], C bf16 [M,N].
+ * K must be a multiple of 16 and A, B 16-byte aligned (TMA requirements).
+ * Replaces launch_w8a8_gemm_v5, w8a8_gemm_v5.hip:128-145. */
+DSV4_API int launch_w8a8_gemm(const void* A, const void* B, const void* sa, const void* sb, void* C, int M,
+                     int N, int K, dsv4_stream_t stream);
+DSV4_API int launch_w8a8_gemm_v5(const void* A, const void* B, const void* sa, const void* sb, void* C,
+                        int M, int N, int K, dsv4_stream_t stream);
+
+/* Raw accumulators: C int32 [M,N] = sum_k A[m,k]*B[n,k].  The product torch._int_mm
+ * supplies in w8a8_gemm_intmm_fused.hip:38-39. */
+DSV4_API int launch_w8a8_gemm_i32(const void* A, const void* B, void* C, int M, int N, int K,
+                         dsv4_stream_t stream);
+
+/* bf_out[m,n] = bf16((float(int_out[m,n]) * sa[m]) * sb[n]).
+ * Replaces launch_scale_convert, w8a8_gemm_intmm_fused.hip:40-52. */
+DSV4_API int launch_scale_convert(const void* int_out, const void* sa, const void* sb, void* bf_out, int M,
+                         int N, dsv4_stream_t stream);
+
+/* ---- MoE grouped GEMM ----------------------------------------------------------- */
+
+/* Rows of A are sorted by expert; expert e owns rows [expert_offsets[e], expert_offsets[e+1])
+ * (int32, on the device, E+1 entries, non-decreasing, last = R).
+ *   sa_groups == 1 : C[r,n] = bf16((float(acc[r,n]) * sa[r]) * sw[e,n])
+ *   sa_groups == K/128 : sa is [R, K/128];
+ *       C[r,n] = bf16(y * sw[e,n]),  y = fma(float(acc_g[r,n]), sa[r,g], y) for g = 0,1,...
+ *       where acc_g is the exact int32 sum over the g-th 128 columns of K.
+ * A int8 [R,K]; W int8 [E,N,K]; sw fp32 [E,N]; C bf16 [R,N].
+ * The reference lists grouped_gemm without source (README.md:66); the layout follows its
+ * engine-side description (DSV4_OPERATOR_ANALYSIS.md:42-43). */
+DSV4_API int launch_grouped_gemm(const void* A, const void* W, const void* sa, const void* sw,
+                        const int* expert_offsets, void* C, int R, int E, int N, int K,
+                        int sa_groups, dsv4_stream_t stream);
+
+/* Segment offsets and the token permutation from top-k routing ids.
+ * topk_ids int32 [T, topk] with values in [0,E) -> expert_offsets int32 [E+1];
+ * src_row int32 [T*topk]: routed row r (in expert-sorted order) came from token src_row[r];
+ * dst_slot int32 [T*topk]: pair (t, j) landed at routed row dst_slot[t*topk + j].
+ * Within an expert, rows keep increasing (t, j) order.  Uses no scratch memory. */
+DSV4_API int launch_moe_segments(const int* topk_ids, int T, int topk, int E, int* expert_offsets,
+                        int* src_row, int* dst_slot, dsv4_stream_t stream);
+
+/* dst[r, :] = src[src_row[r], :] for r < R, rows of row_bytes bytes (multiple of 16);
+ * optionally the same gather for fp32 scales with scales_per_row entries per row. */
+DSV4_API int launch_gather_rows(const void* src, const int* src_row, void* dst, int R, int row_bytes,
+                       const float* src_scale, float* dst_scale, int scales_per_row,
+                       dsv4_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSV4_W8A8_H */

@@ -1,0 +1,163 @@
+"""ctypes front end of the C oracle (oracle/w8a8_oracle.c).  Test infrastructure only.
+
+All functions take and return CPU torch tensors (bf16 / int8 / float32 / int32) so that
+a test can feed the same seeded tensors to the oracle and, after .cuda(), to the kernels.
+"""
+import ctypes
+import functools
+
+import torch
+
+from . import build_oracle
+
+_c_i8p = ctypes.c_void_p
+
+
+@functools.lru_cache(maxsize=1)
+def lib() -> ctypes.CDLL:
+    path = build_oracle.build()
+    L = ctypes.CDLL(path)
+    L.oracle_exp.restype = ctypes.c_float
+    L.oracle_exp.argtypes = [ctypes.c_float]
+    return L
+
+
+def _p(t: torch.Tensor) -> ctypes.c_void_p:
+    assert t.device.type == "cpu" and t.is_contiguous(), "oracle takes contiguous CPU tensors"
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _rows(x: torch.Tensor):
+    n = x.shape[-1]
+    return (x.numel() // n if n else 0), n
+
+
+def per_token_quant_int8(x: torch.Tensor, divide_form: bool = False):
+    """-> (q int8 like x, s float32 [M,1]).  divide_form=True uses round(x/s) clamped to +-127."""
+    assert x.dtype == torch.bfloat16
+    x = x.contiguous()
+    m, n = _rows(x)
+    q = torch.empty(x.shape, dtype=torch.int8)
+    s = torch.empty(m, dtype=torch.float32)
+    fn = lib().oracle_ptq_divide_form if divide_form else lib().oracle_ptq
+    fn(_p(x), ctypes.c_int64(n), _p(q), _p(s), ctypes.c_int(m), ctypes.c_int(n))
+    return q, s.unsqueeze(-1)
+
+
+def per_token_group_quant_int8(x: torch.Tensor, group_size: int):
+    """-> (q int8 like x, s float32 [M, ceil(N/group_size)])."""
+    assert x.dtype == torch.bfloat16
+    x = x.contiguous()
+    m, n = _rows(x)
+    g = (n + group_size - 1) // group_size
+    q = torch.empty(x.shape, dtype=torch.int8)
+    s = torch.empty((m, g), dtype=torch.float32)
+    lib().oracle_ptgq(_p(x), _p(q), _p(s), ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(group_size))
+    return q, s
+
+
+def add_rmsnorm_quant(res: torch.Tensor, x: torch.Tensor, w: torch.Tensor, eps: float):
+    """Mutates res (res <- res + x) like the operator; -> (q, s [M,1])."""
+    assert res.dtype == x.dtype == w.dtype == torch.bfloat16 and res.is_contiguous()
+    x = x.contiguous()
+    w = w.contiguous()
+    m, n = _rows(x)
+    q = torch.empty(x.shape, dtype=torch.int8)
+    s = torch.empty(m, dtype=torch.float32)
+    lib().oracle_add_rmsnorm_quant(_p(res), _p(x), _p(w), _p(q), _p(s), ctypes.c_int(m), ctypes.c_int(n),
+                                   ctypes.c_float(eps))
+    return q, s.unsqueeze(-1)
+
+
+def rmsnorm(x: torch.Tensor, eps: float):
+    """In place, no gamma; returns x."""
+    assert x.dtype == torch.bfloat16 and x.is_contiguous()
+    m, n = _rows(x)
+    lib().oracle_rmsnorm(_p(x), ctypes.c_int(m), ctypes.c_int(n), ctypes.c_float(eps))
+    return x
+
+
+def _gate_up(gate, up):
+    assert gate.dtype == up.dtype == torch.bfloat16 and gate.dim() == 2 and gate.shape == up.shape
+    assert gate.stride(1) == 1 and up.stride(1) == 1
+    return gate.shape[0], gate.shape[1], gate.stride(0), up.stride(0)
+
+
+def silu_and_mul(gate: torch.Tensor, up: torch.Tensor):
+    m, n, ldg, ldu = _gate_up(gate, up)
+    out = torch.empty((m, n), dtype=torch.bfloat16)
+    lib().oracle_silu_mul(ctypes.c_void_p(gate.data_ptr()), ctypes.c_int64(ldg), ctypes.c_void_p(up.data_ptr()),
+                          ctypes.c_int64(ldu), _p(out), ctypes.c_int(m), ctypes.c_int(n))
+    return out
+
+
+def silu_mul_quant(gate: torch.Tensor, up: torch.Tensor, mask: torch.Tensor = None, q=None, s=None):
+    """gate/up may be row-strided halves of a packed [M,2N] tensor.  -> (q, s [M,1])."""
+    m, n, ldg, ldu = _gate_up(gate, up)
+    if q is None:
+        q = torch.zeros((m, n), dtype=torch.int8)
+    if s is None:
+        s = torch.zeros(m, dtype=torch.float32)
+    s_flat = s.view(-1)
+    mp = ctypes.c_void_p(0) if mask is None else _p(mask.to(torch.int32).contiguous())
+    lib().oracle_silu_mul_quant(ctypes.c_void_p(gate.data_ptr()), ctypes.c_int64(ldg),
+                                ctypes.c_void_p(up.data_ptr()), ctypes.c_int64(ldu), mp, _p(q), _p(s_flat),
+                                ctypes.c_int(m), ctypes.c_int(n))
+    return q, s_flat.unsqueeze(-1)
+
+
+def gemm_i32(A: torch.Tensor, B: torch.Tensor):
+    assert A.dtype == B.dtype == torch.int8
+    A, B = A.contiguous(), B.contiguous()
+    m, k = A.shape
+    n = B.shape[0]
+    C = torch.empty((m, n), dtype=torch.int32)
+    lib().oracle_gemm_i32(_p(A), _p(B), _p(C), ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k))
+    return C
+
+
+def scale_convert(acc: torch.Tensor, sa: torch.Tensor, sb: torch.Tensor):
+    m, n = acc.shape
+    out = torch.empty((m, n), dtype=torch.bfloat16)
+    lib().oracle_scale_convert(_p(acc.contiguous()), _p(sa.contiguous().view(-1).float()),
+                               _p(sb.contiguous().view(-1).float()), _p(out), ctypes.c_int(m), ctypes.c_int(n))
+    return out
+
+
+def w8a8_gemm(A, B, sa, sb):
+    A, B = A.contiguous(), B.contiguous()
+    m, k = A.shape
+    n = B.shape[0]
+    out = torch.empty((m, n), dtype=torch.bfloat16)
+    lib().oracle_w8a8_gemm(_p(A), _p(B), _p(sa.contiguous().view(-1)), _p(sb.contiguous().view(-1)), _p(out),
+                           ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k))
+    return out
+
+
+def grouped_gemm(A, W, sa, sw, expert_offsets):
+    """A int8 [R,K] sorted by expert, W int8 [E,N,K], sa [R] / [R,1] or [R,K/128], sw [E,N]."""
+    A, W = A.contiguous(), W.contiguous()
+    r, k = A.shape
+    e, n, _ = W.shape
+    sa = sa.contiguous().float()
+    groups = 1 if sa.numel() == r else sa.shape[-1]
+    out = torch.zeros((r, n), dtype=torch.bfloat16)
+    lib().oracle_grouped_gemm(_p(A), _p(W), _p(sa), _p(sw.contiguous()), _p(expert_offsets.to(torch.int32).contiguous()),
+                              _p(out), ctypes.c_int(r), ctypes.c_int(e), ctypes.c_int(n), ctypes.c_int(k),
+                              ctypes.c_int(groups))
+    return out
+
+
+def moe_segments(topk_ids: torch.Tensor, num_experts: int):
+    ids = topk_ids.to(torch.int32).contiguous()
+    t, topk = ids.shape
+    off = torch.empty(num_experts + 1, dtype=torch.int32)
+    src = torch.empty(t * topk, dtype=torch.int32)
+    dst = torch.empty(t * topk, dtype=torch.int32)
+    lib().oracle_moe_segments(_p(ids), ctypes.c_int(t), ctypes.c_int(topk), ctypes.c_int(num_experts), _p(off),
+                              _p(src), _p(dst))
+    return off, src, dst
+
+
+def exp_fixed(x: float) -> float:
+    return float(lib().oracle_exp(ctypes.c_float(x)))

@@ -1,0 +1,167 @@
+"""GPU parity of the int8 GEMM (dense and grouped) against the CPU oracle.
+int32 accumulators bit-exact; bf16 outputs are compared bit-exact too (the epilogue is a
+fixed sequence of rounded operations) and, as the stated bar, within 1e-2 of the output's
+absolute maximum."""
+import pytest
+import torch
+
+from bw1000_dsv4_kernels_b200 import workloads as wl
+from oracle import cpu as oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL_REL_TO_ABSMAX = 1e-2
+
+
+def _operands(m, n, k, seed):
+    A = wl.int8_weights((m, k), seed=seed)
+    B = wl.int8_weights((n, k), seed=seed + 1)
+    sa = wl.channel_scales((m,), seed=seed + 2) * 3.0
+    sb = wl.channel_scales((n,), seed=seed + 3)
+    return A, B, sa, sb
+
+
+def _check_bf16(out, ref, what):
+    out, ref = out.cpu(), ref.cpu()
+    assert out.shape == ref.shape
+    absmax = ref.float().abs().max().item()
+    err = (out.float() - ref.float()).abs().max().item()
+    assert err <= TOL_REL_TO_ABSMAX * max(absmax, 1e-30), f"{what}: max abs err {err} vs absmax {absmax}"
+    bad = (out.view(torch.int16) != ref.view(torch.int16)).sum().item()
+    assert bad == 0, f"{what}: {bad} of {out.numel()} bf16 outputs differ in bits"
+
+
+SHAPES = [
+    (128, 256, 128),     # one tile, one k-block
+    (128, 256, 512),     # one tile, several k-blocks (ring wraps at 4 stages)
+    (256, 512, 1024),    # several tiles per CTA? no: 4 tiles over 4 CTAs
+    (1, 4096, 7168),     # decode row
+    (16, 4096, 7168),
+    (64, 4096, 7168),
+    (256, 4096, 7168),
+    (100, 200, 304),     # ragged M, N; K not a multiple of 128
+    (130, 264, 2064),    # ragged last tiles in both dimensions
+    (5, 72, 16),         # smallest K
+    (300, 1000, 4096),
+    (64, 7168, 18432),   # down projection, long K: |acc| exceeds 2^24
+]
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_gemm_i32_bit_exact(cabi, m, n, k):
+    A, B, _, _ = _operands(m, n, k, seed=m + n + k)
+    ref = oracle.gemm_i32(A, B)
+    out = cabi.w8a8_gemm_i32(A.cuda(), B.cuda())
+    assert cabi.device_status() == 0
+    bad = (out.cpu() != ref).sum().item()
+    assert bad == 0, f"{bad} of {ref.numel()} int32 accumulators differ"
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_w8a8_gemm_matches_oracle(cabi, ext, m, n, k):
+    A, B, sa, sb = _operands(m, n, k, seed=m + n + k)
+    ref = oracle.w8a8_gemm(A, B, sa, sb)
+    out = cabi.w8a8_gemm(A.cuda(), B.cuda(), sa.cuda(), sb.cuda())
+    assert cabi.device_status() == 0
+    _check_bf16(out, ref, "C-ABI")
+    out2 = ext.w8a8_scaled_gemm(A.cuda(), B.cuda(), sa.cuda().unsqueeze(-1), sb.cuda())
+    _check_bf16(out2, ref, "operator")
+    out3 = ext.w8a8_gemm(A.cuda(), B.cuda(), sa.cuda(), sb.cuda())
+    _check_bf16(out3, ref, "alias")
+
+
+def test_gemm_many_tiles_per_cta(cabi):
+    # 2048 x 4096 -> 256 tiles of 128x256 on 148 CTAs: every CTA loops, both accumulators cycle
+    m, n, k = 2048, 4096, 1024
+    A, B, sa, sb = _operands(m, n, k, seed=1)
+    ref = oracle.w8a8_gemm(A, B, sa, sb)
+    out = cabi.w8a8_gemm(A.cuda(), B.cuda(), sa.cuda(), sb.cuda())
+    assert cabi.device_status() == 0
+    _check_bf16(out, ref, "2048x4096x1024")
+
+
+def test_gemm_extreme_values_no_overflow_surprise(cabi):
+    # all operands at +-127/-128: the largest magnitudes the accumulator can see
+    m, n, k = 128, 256, 18432
+    A = torch.full((m, k), 127, dtype=torch.int8)
+    B = torch.full((n, k), 127, dtype=torch.int8)
+    B[::2] = -128
+    ref = oracle.gemm_i32(A, B)
+    out = cabi.w8a8_gemm_i32(A.cuda(), B.cuda())
+    assert (out.cpu() != ref).sum().item() == 0
+    sa = torch.full((m,), 1e-3)
+    sb = torch.full((n,), 1e-3)
+    _check_bf16(cabi.w8a8_gemm(A.cuda(), B.cuda(), sa.cuda(), sb.cuda()), oracle.w8a8_gemm(A, B, sa, sb), "extremes")
+
+
+def test_scale_convert_matches_oracle(cabi, ext):
+    m, n = 37, 1000
+    acc = torch.randint(-(2 ** 28), 2 ** 28, (m, n), dtype=torch.int32, generator=torch.Generator().manual_seed(3))
+    sa = wl.channel_scales((m,), seed=1)
+    sb = wl.channel_scales((n,), seed=2)
+    ref = oracle.scale_convert(acc, sa, sb)
+    _check_bf16(cabi.scale_convert(acc.cuda(), sa.cuda(), sb.cuda()), ref, "C-ABI")
+    _check_bf16(ext.scale_convert(acc.cuda(), sa.cuda(), sb.cuda()), ref, "operator")
+
+
+def test_linearity_at_full_size(cabi):
+    # size-independent property at the benchmark's largest dense shape: the int32 product is
+    # linear in A, so (A1 + A2) B^T == A1 B^T + A2 B^T exactly when A1 + A2 stays in int8
+    m, n, k = 2048, 4096, 7168
+    g = torch.Generator(device="cuda").manual_seed(0)
+    A1 = torch.randint(-60, 61, (m, k), dtype=torch.int8, device="cuda", generator=g)
+    A2 = torch.randint(-60, 61, (m, k), dtype=torch.int8, device="cuda", generator=g)
+    B = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda", generator=g)
+    c12 = cabi.w8a8_gemm_i32(A1 + A2, B)
+    c1 = cabi.w8a8_gemm_i32(A1, B)
+    c2 = cabi.w8a8_gemm_i32(A2, B)
+    assert cabi.device_status() == 0
+    assert torch.equal(c12, c1 + c2)
+    # and a sampled block against the oracle
+    ref = oracle.gemm_i32(A1[:64].cpu(), B[:512].cpu())
+    assert torch.equal(c1[:64, :512].cpu(), ref)
+
+
+def test_gemm_argument_errors(cabi, ext):
+    A = torch.zeros((4, 24), dtype=torch.int8, device="cuda")
+    B = torch.zeros((8, 24), dtype=torch.int8, device="cuda")
+    s = torch.ones(8, device="cuda")
+    with pytest.raises(RuntimeError, match="multiple of 16"):
+        ext.w8a8_scaled_gemm(A, B, s[:4], s)
+    with pytest.raises(RuntimeError):
+        ext.w8a8_scaled_gemm(A.cpu(), B.cpu(), s[:4].cpu(), s.cpu())
+    with pytest.raises(RuntimeError):
+        ext.w8a8_scaled_gemm(A.float(), B, s[:4], s)
+    out = ext.w8a8_scaled_gemm(torch.zeros((0, 32), dtype=torch.int8, device="cuda"),
+                               torch.zeros((8, 32), dtype=torch.int8, device="cuda"), s[:0], s)
+    assert out.shape == (0, 8)
+
+
+# ---- grouped GEMM ---------------------------------------------------------------------
+def _grouped_case(seg_lens, n, k, seed):
+    e = len(seg_lens)
+    off = torch.zeros(e + 1, dtype=torch.int32)
+    off[1:] = torch.cumsum(torch.tensor(seg_lens), 0)
+    r = int(off[-1])
+    A = wl.int8_weights((r, k), seed=seed)
+    W = wl.int8_weights((e, n, k), seed=seed + 1)
+    sa = wl.channel_scales((r,), seed=seed + 2) * 3.0
+    sw = wl.channel_scales((e, n), seed=seed + 3)
+    return A, W, sa, sw, off
+
+
+@pytest.mark.parametrize("seg_lens,n,k", [
+    ([128, 128], 256, 256),
+    ([5, 0, 300, 128, 1, 0, 77], 512, 384),
+    ([130] * 16, 1024, 512),
+    ([0, 0, 9], 72, 64),
+    ([64, 200, 17, 129, 255, 3, 0, 90], 4096, 7168),
+])
+def test_grouped_gemm_matches_oracle(cabi, ext, seg_lens, n, k):
+    A, W, sa, sw, off = _grouped_case(seg_lens, n, k, seed=len(seg_lens) + n)
+    ref = oracle.grouped_gemm(A, W, sa, sw, off)
+    out = cabi.grouped_gemm(A.cuda(), W.cuda(), sa.cuda(), sw.cuda(), off.cuda())
+    assert cabi.device_status() == 0
+    _check_bf16(out, ref, "C-ABI")
+    out2 = ext.grouped_gemm(A.cuda(), W.cuda(), sa.cuda().unsqueeze(-1), sw.cuda(), off.cuda())
+    _check_bf16(out2, ref, "operator")
