@@ -58,6 +58,7 @@ struct Params {
     void* C;
     const int* offsets;  // null: dense
     int M, N, K, E;
+    int64_t ldc;         // row stride of C in elements (>= N)
     int sa_groups;
     int out_i32;
 };
@@ -137,6 +138,68 @@ struct Scheduler {
 
 __device__ __forceinline__ void report_wait_failure(int site) {
     atomicCAS(&g_device_status, 0, site);
+}
+
+
+// Drains one finished accumulator: this thread owns TMEM lane (= tile row) `row` and walks
+// NCOLS columns 32 at a time: tcgen05.ld -> (float(acc) * sa) * sb[col] -> bf16 -> global.
+// `sbs` holds the tile's column scales in shared memory (private to the warp).
+template <int NCOLS>
+__device__ __forceinline__ void drain_accumulator(const Params& p, uint32_t t_lane, const float* sbs, int row,
+                                                  bool row_ok, int n0, bool vec_ok) {
+    const float sa = (row_ok && !p.out_i32) ? __ldg(p.sa + row) : 0.0f;
+#pragma unroll 1
+    for (int cc = 0; cc < NCOLS / 32; ++cc) {
+        uint32_t r[32];
+        __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the stores
+        ptx::tmem_ld_32x32b_x32(t_lane + cc * 32, r);
+        ptx::tmem_ld_wait();
+        const int n = n0 + cc * 32;
+        if (!row_ok || n >= p.N) continue;
+        if (p.out_i32) {
+            int* out = static_cast<int*>(p.C) + (int64_t)row * p.ldc + n;
+            if (vec_ok && n + 32 <= p.N) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<uint4*>(out + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (n + j < p.N) out[j] = (int)r[j];
+            }
+        } else {
+            __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.C) + (int64_t)row * p.ldc + n;
+            const float4* sb4 = reinterpret_cast<const float4*>(sbs + cc * 32);
+            uint32_t packed[16];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 s4 = sb4[j];
+                const float v0 = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 0]), sa), s4.x);
+                const float v1 = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 1]), sa), s4.y);
+                const float v2 = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 2]), sa), s4.z);
+                const float v3 = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 3]), sa), s4.w);
+                packed[2 * j] = pack_bf16x2_rn(v0, v1);
+                packed[2 * j + 1] = pack_bf16x2_rn(v2, v3);
+            }
+            if (vec_ok && n + 32 <= p.N) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    *reinterpret_cast<uint4*>(out + 8 * j) =
+                        make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const uint32_t w = packed[j >> 1];
+                    const uint16_t h = (j & 1) ? (uint16_t)(w >> 16) : (uint16_t)(w & 0xffffu);
+                    if (n + j < p.N) reinterpret_cast<uint16_t*>(out)[j] = h;
+                }
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ bool c_vector_stores_ok(const Params& p) {
+    return (p.N % 8 == 0) && (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
 }
 
 // ------------------------------------------------------------------------------------
@@ -284,7 +347,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         float* sbs = sb_tile + (warp - 2) * BN;  // private to this warp: no block-level barrier
         int acc = 0;
         uint32_t acc_phase = 0;
-        const bool vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+        const bool vec_ok = c_vector_stores_ok(p);
         for (int t = blockIdx.x; t < sched.total; t += gridDim.x) {
             const TileCoord c = sched.at(t, BN);
             // column scales of this tile -> this warp's shared copy
@@ -303,57 +366,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             ptx::tc_fence_after_sync();
             const int row = c.a_row0 + quarter * 32 + lane;
-            const bool row_ok = row < c.row_end;
-            const float sa = (row_ok && !p.out_i32) ? __ldg(p.sa + row) : 0.0f;
             const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-#pragma unroll 1
-            for (int cc = 0; cc < BN / 32; ++cc) {
-                uint32_t r[32];
-                __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the stores
-                ptx::tmem_ld_32x32b_x32(t_lane + cc * 32, r);
-                ptx::tmem_ld_wait();
-                const int n = c.n0 + cc * 32;
-                if (!row_ok || n >= p.N) continue;
-                if (p.out_i32) {
-                    int* out = static_cast<int*>(p.C) + (int64_t)row * p.N + n;
-                    if (vec_ok && n + 32 <= p.N) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<uint4*>(out + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (n + j < p.N) out[j] = (int)r[j];
-                    }
-                } else {
-                    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.C) + (int64_t)row * p.N + n;
-                    const float4* sb4 = reinterpret_cast<const float4*>(sbs + cc * 32);
-                    uint32_t packed[16];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float4 s4 = sb4[j];
-                        const float v0 = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 0]), sa), s4.x);
-                        const float v1 = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 1]), sa), s4.y);
-                        const float v2 = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 2]), sa), s4.z);
-                        const float v3 = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 3]), sa), s4.w);
-                        packed[2 * j] = pack_bf16x2_rn(v0, v1);
-                        packed[2 * j + 1] = pack_bf16x2_rn(v2, v3);
-                    }
-                    if (vec_ok && n + 32 <= p.N) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            *reinterpret_cast<uint4*>(out + 8 * j) =
-                                make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const uint32_t w = packed[j >> 1];
-                            const uint16_t h = (j & 1) ? (uint16_t)(w >> 16) : (uint16_t)(w & 0xffffu);
-                            if (n + j < p.N) reinterpret_cast<uint16_t*>(out)[j] = h;
-                        }
-                    }
-                }
-            }
+            drain_accumulator<BN>(p, t_lane, sbs, row, row < c.row_end, c.n0, vec_ok);
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(acc_empty_bar(acc));
@@ -368,6 +382,199 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (warp == 1) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+
+// ------------------------------------------------------------------------------------
+// CTA-pair kernel (dense GEMM, M > 128): a cluster of two CTAs owns a 256 x 256 output
+// tile.  CTA r of the pair loads rows [256*mt + 128*r, +128) of A and rows
+// [256*nt + 128*r, +128) of B, so a 128-deep K block costs each SM 32 KB of L2 traffic
+// instead of 48 KB for the same number of MMA cycles.  The even CTA issues
+// tcgen05.mma.cta_group::2 (M256 x N256 x K32) for both; each CTA drains the accumulator of
+// its own 128 rows from its own tensor memory.
+//   full[s]      lives in the even CTA; both CTAs' tile loads complete on it
+//   empty[s]     one in each CTA; the even CTA's commit arrives on both
+//   acc_full[a]  one in each CTA; the even CTA's commit arrives on both
+//   acc_empty[a] lives in the even CTA; the drain warps of both CTAs arrive on it
+// ------------------------------------------------------------------------------------
+template <int STAGES>
+struct PairSmem {
+    static constexpr int kABytes = BM * BK;        // this CTA's 128 rows of A
+    static constexpr int kBBytes = 128 * BK;       // this CTA's 128 of the tile's 256 rows of B
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTilesBytes = STAGES * kStageBytes;
+    static constexpr int kSbOff = kTilesBytes;                  // 4 warps x 256 column scales
+    static constexpr int kBarOff = kSbOff + 4 * 256 * 4;        // 8-byte aligned
+    static constexpr int kNumBars = 2 * STAGES + 4;
+    static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
+    static constexpr int kAbortOff = kTmemSlotOff + 4;
+    static constexpr int kTotal = kAbortOff + 4;
+    static constexpr int kDynamic = kTotal + 1024;
+};
+
+template <int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const Params p) {
+    using L = PairSmem<STAGES>;
+    constexpr int PBN = 256;  // tile width of the pair
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float* sb_tile = reinterpret_cast<float*>(smem + L::kSbOff);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlotOff);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
+
+    const uint32_t tiles_base = ptx::smem_u32(smem);
+    const uint32_t bar_base = ptx::smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_ctarank();
+    constexpr uint32_t kTmemCols = 512;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(acc_full_bar(a), 1);
+            ptx::mbar_init(acc_empty_bar(a), 2 * (kDrainThreads / 32));  // drain warps of both CTAs
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+        ptx::prefetch_tensormap(&tmA);
+        ptx::prefetch_tensormap(&tmB);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();  // the peer's barriers exist before anything arrives on them
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int tiles_m = (p.M + 255) / 256;
+    const int tiles_n = (p.N + PBN - 1) / PBN;
+    const int total = tiles_m * tiles_n;
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int k_blocks = (p.K + BK - 1) / BK;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        if (ptx::elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair; t < total && ok; t += npairs) {
+                const int mt = t % tiles_m, nt = t / tiles_m;
+                const int a_row0 = mt * 256 + (int)rank * 128;
+                const int b_row0 = nt * PBN + (int)rank * 128;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u) || *abort_flag) {
+                        report_wait_failure(kWaitEmptyStage);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = tiles_base + stage * L::kStageBytes;
+                    const uint32_t b_dst = a_dst + L::kABytes;
+                    const uint32_t leader_full = ptx::map_to_cta(full_bar(stage), 0);
+                    if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * L::kStageBytes);
+                    ptx::tma_load_2d_pair(a_dst, &tmA, kb * BK, a_row0, leader_full);
+                    ptx::tma_load_2d_pair(b_dst, &tmB, kb * BK, b_row0, leader_full);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (even CTA only) ----------------
+        if (rank == 0 && ptx::elect_one()) {
+            constexpr uint32_t idesc = ptx::idesc_i8(256, PBN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int t = pair; t < total && ok; t += npairs) {
+                if (!ptx::mbar_wait_bounded(acc_empty_bar(acc), acc_phase ^ 1u) || *abort_flag) {
+                    report_wait_failure(kWaitAccEmpty);
+                    *abort_flag = 1;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * PBN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!ptx::mbar_wait_bounded(full_bar(stage), phase) || *abort_flag) {
+                        report_wait_failure(kWaitFullStage);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_src = tiles_base + stage * L::kStageBytes;
+                    const uint64_t adesc = ptx::smem_desc_k_sw128(a_src);
+                    const uint64_t bdesc = ptx::smem_desc_k_sw128(a_src + L::kABytes);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        ptx::mma_i8_ss_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    ptx::tc_commit_pair(empty_bar(stage), 0x3);  // frees the stage in both CTAs
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                ptx::tc_commit_pair(acc_full_bar(acc), 0x3);
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ---------------- drain warps (both CTAs) ----------------
+        const int quarter = warp & 3;
+        float* sbs = sb_tile + (warp - 2) * PBN;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        const bool vec_ok = c_vector_stores_ok(p);
+        for (int t = pair; t < total; t += npairs) {
+            const int mt = t % tiles_m, nt = t / tiles_m;
+            const int n0 = nt * PBN;
+            __syncwarp();
+            if (!p.out_i32) {
+                for (int j = lane; j < PBN; j += 32) sbs[j] = (n0 + j < p.N) ? __ldg(p.sb + n0 + j) : 0.0f;
+            }
+            __syncwarp();
+            if (!ptx::mbar_wait_bounded(acc_full_bar(acc), acc_phase) || *abort_flag) {
+                report_wait_failure(kWaitAccFull);
+                *abort_flag = 1;
+                break;
+            }
+            ptx::tc_fence_after_sync();
+            const int row = mt * 256 + (int)rank * 128 + quarter * 32 + lane;
+            const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * PBN;
+            drain_accumulator<PBN>(p, t_lane, sbs, row, row < p.M, n0, vec_ok);
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+
+    // ---------------- teardown ----------------
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();  // neither CTA leaves while the other may still touch its memory
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
     }
 }
 
@@ -447,6 +654,27 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params&
     return check_launch("w8a8_gemm");
 }
 
+template <int STAGES>
+int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, cudaStream_t st) {
+    using L = PairSmem<STAGES>;
+    static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
+    static bool opted_in[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !opted_in[dev]) {
+        if (cudaFuncSetAttribute(gemm_i8_pair_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 L::kDynamic) != cudaSuccess)
+            return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: cannot raise the dynamic shared memory limit");
+        if (dev >= 0 && dev < 64) opted_in[dev] = true;
+    }
+    const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
+    int pairs = sm_count() / 2;
+    if (pairs <= 0) return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: no CUDA device");
+    if (tiles < pairs) pairs = tiles;
+    gemm_i8_pair_kernel<STAGES><<<2 * pairs, kThreads, L::kDynamic, st>>>(tmA, tmB, p);
+    return check_launch("w8a8_gemm");
+}
+
 }  // namespace
 
 int gemm_i8(const GemmArgs& a, cudaStream_t st) {
@@ -465,7 +693,9 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
     Params p;
     p.sa = a.sa; p.sb = a.sb; p.C = a.C; p.offsets = a.offsets;
     p.M = a.M; p.N = a.N; p.K = a.K; p.E = grouped ? a.E : 1;
+    p.ldc = a.ldc > 0 ? a.ldc : a.N;
     p.sa_groups = a.sa_groups; p.out_i32 = a.out_i32;
+    if (p.ldc < a.N) return fail(DSV4_ERR_ARG, "w8a8_gemm: ldc smaller than N");
 
     const uint64_t b_rows = grouped ? (uint64_t)a.E * a.N : (uint64_t)a.N;
     const int sms = sm_count();
@@ -479,6 +709,14 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
     if (bn == 64 && (int64_t)tiles_m_bound * ((a.N + 63) / 64) < sms) bn = 32;
 
     CUtensorMap tmA, tmB;
+    // Dense problems with more than one 128-row tile go to the CTA-pair kernel
+    if (!grouped && a.M > 128 && (int64_t)((a.M + 255) / 256) * ((a.N + 255) / 256) >= sms / 4) {
+        int rc2 = make_tile_map(&tmA, a.A, (uint64_t)a.M, (uint64_t)a.K, BM);
+        if (rc2) return rc2;
+        rc2 = make_tile_map(&tmB, a.B, b_rows, (uint64_t)a.K, 128);
+        if (rc2) return rc2;
+        return launch_pair_variant<6>(tmA, tmB, p, st);
+    }
     int rc = make_tile_map(&tmA, a.A, (uint64_t)a.M, (uint64_t)a.K, BM);
     if (rc) return rc;
     rc = make_tile_map(&tmB, a.B, b_rows, (uint64_t)a.K, (uint32_t)bn);

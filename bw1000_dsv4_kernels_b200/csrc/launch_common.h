@@ -32,6 +32,7 @@ struct GemmArgs {
     void* C;              // bf16 [M, N] or int32 [M, N]
     const int* offsets;   // null for a dense GEMM, else expert_offsets[E+1]
     int M, N, K, E;
+    int64_t ldc;          // row stride of C in elements; 0 = N
     int sa_groups;        // 1 = per-token scale; K/128 = one scale per 128 of K
     int out_i32;          // 1 = write raw int32 accumulators
 };

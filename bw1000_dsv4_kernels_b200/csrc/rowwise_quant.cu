@@ -43,8 +43,10 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
 
 __device__ __forceinline__ uint2 quant8_rn(const float (&f)[8], float inv) {
     uint2 o;
-    o.x = pack_i8x4(quant_rn(f[0], inv), quant_rn(f[1], inv), quant_rn(f[2], inv), quant_rn(f[3], inv));
-    o.y = pack_i8x4(quant_rn(f[4], inv), quant_rn(f[5], inv), quant_rn(f[6], inv), quant_rn(f[7], inv));
+    o.x = pack_lowbytes(quant_rn_lowbyte(f[0], inv), quant_rn_lowbyte(f[1], inv), quant_rn_lowbyte(f[2], inv),
+                        quant_rn_lowbyte(f[3], inv));
+    o.y = pack_lowbytes(quant_rn_lowbyte(f[4], inv), quant_rn_lowbyte(f[5], inv), quant_rn_lowbyte(f[6], inv),
+                        quant_rn_lowbyte(f[7], inv));
     return o;
 }
 
@@ -392,53 +394,65 @@ __global__ void __launch_bounds__(kSumLanes) rmsnorm_generic_kernel(__nv_bfloat1
 // gate and up may be the two halves of one packed [M, 2N] tensor: ldg/ldu are row
 // strides in elements.
 // ====================================================================================
-template <int VPT, int MAXT>
-__global__ void __launch_bounds__(MAXT) silu_mul_quant_vec_kernel(
+// One CTA per row.  h = silu(g)*u is computed once, in fp32, and parked in shared memory
+// (N floats) between the amax reduction and the quantisation, so that registers only hold
+// the loads in flight and several rows are resident per SM.  The arithmetic runs on
+// float2 lanes (packed f32x2 instructions).
+template <int T, int MINB>
+__global__ void __launch_bounds__(T, MINB) silu_mul_quant_vec_kernel(
     const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
     const int* __restrict__ mask, int8_t* __restrict__ q, float* __restrict__ s, int M, int N,
     int64_t ldg, int64_t ldu) {
+    extern __shared__ float4 h_row4[];  // N floats, 16-byte aligned
     __shared__ float red[32];
-    const int V = N >> 3, T = blockDim.x, tid = threadIdx.x;
+    const int V = N >> 3, tid = threadIdx.x;
     for (int row = blockIdx.x; row < M; row += gridDim.x) {
         if (mask != nullptr && mask[row] == 0) continue;  // uniform over the block
         const uint4* gr = reinterpret_cast<const uint4*>(g + (int64_t)row * ldg);
         const uint4* ur = reinterpret_cast<const uint4*>(u + (int64_t)row * ldu);
-        uint4 gv[VPT], uv[VPT];
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int idx = tid + i * T;
-            if (idx < V) {
-                gv[i] = ld_stream(gr + idx);
-                uv[i] = ld_stream(ur + idx);
-            } else {
-                gv[i] = make_uint4(0, 0, 0, 0);
-                uv[i] = make_uint4(0, 0, 0, 0);
-            }
-        }
-        float h[VPT][8];
         float am = 0.0f;
+        for (int base = tid; base < V; base += 2 * T) {
+            // two vectors of each operand in flight per thread
+            const int idx1 = base + T;
+            const uint4 g0 = ld_stream(gr + base), u0 = ld_stream(ur + base);
+            uint4 g1 = make_uint4(0, 0, 0, 0), u1 = g1;
+            if (idx1 < V) {
+                g1 = ld_stream(gr + idx1);
+                u1 = ld_stream(ur + idx1);
+            }
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            float g8[8], u8[8];
-            unpack8(gv[i], g8);
-            unpack8(uv[i], u8);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                h[i][e] = silu_mul(g8[e], u8[e]);
-                am = fmaxf(am, fabsf(h[i][e]));
+            for (int half = 0; half < 2; ++half) {
+                const uint4 gv = half ? g1 : g0, uv = half ? u1 : u0;
+                const int idx = half ? idx1 : base;
+                if (idx >= V) break;
+                const float2 h0 = silu_mul2(bf16x2_to_f32x2(gv.x), bf16x2_to_f32x2(uv.x));
+                const float2 h1 = silu_mul2(bf16x2_to_f32x2(gv.y), bf16x2_to_f32x2(uv.y));
+                const float2 h2 = silu_mul2(bf16x2_to_f32x2(gv.z), bf16x2_to_f32x2(uv.z));
+                const float2 h3 = silu_mul2(bf16x2_to_f32x2(gv.w), bf16x2_to_f32x2(uv.w));
+                am = fmaxf(am, fmaxf(fmaxf(fabsf(h0.x), fabsf(h0.y)), fmaxf(fabsf(h1.x), fabsf(h1.y))));
+                am = fmaxf(am, fmaxf(fmaxf(fabsf(h2.x), fabsf(h2.y)), fmaxf(fabsf(h3.x), fabsf(h3.y))));
+                h_row4[2 * idx] = make_float4(h0.x, h0.y, h1.x, h1.y);
+                h_row4[2 * idx + 1] = make_float4(h2.x, h2.y, h3.x, h3.y);
             }
         }
-        am = block_max(am, red);
+        am = block_max(am, red);  // also orders the shared-memory writes before the reads below
         float scale, inv;
         scale_from_amax(am, scale, inv);
         if (tid == 0) s[row] = scale;
+        const float2 inv2 = splat2(inv);
         uint2* qr = reinterpret_cast<uint2*>(q + (int64_t)row * N);
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int idx = tid + i * T;
-            if (idx < V) qr[idx] = quant8_rn(h[i], inv);
+        for (int idx = tid; idx < V; idx += T) {
+            const float4 a = h_row4[2 * idx], b = h_row4[2 * idx + 1];
+            const float2 c0 = quant_rn_lowbyte2(make_float2(a.x, a.y), inv2);
+            const float2 c1 = quant_rn_lowbyte2(make_float2(a.z, a.w), inv2);
+            const float2 c2 = quant_rn_lowbyte2(make_float2(b.x, b.y), inv2);
+            const float2 c3 = quant_rn_lowbyte2(make_float2(b.z, b.w), inv2);
+            uint2 o;
+            o.x = pack_lowbytes(__float_as_uint(c0.x), __float_as_uint(c0.y), __float_as_uint(c1.x), __float_as_uint(c1.y));
+            o.y = pack_lowbytes(__float_as_uint(c2.x), __float_as_uint(c2.y), __float_as_uint(c3.x), __float_as_uint(c3.y));
+            qr[idx] = o;
         }
-        __syncthreads();
+        __syncthreads();  // the row buffer and `red` are reused by the next row
     }
 }
 
@@ -626,17 +640,24 @@ int silu_mul_quant(const void* g, const void* u, const int* mask, void* q, void*
     const bool vec = (N % 8 == 0) && (ldg % 8 == 0) && (ldu % 8 == 0) && aligned16(g) &&
                      aligned16(u) && ((reinterpret_cast<uintptr_t>(q) & 7) == 0);
     const int V = N / 8;
-    if (vec && V <= 4096) {
-        if (V <= 256) {
-            const int T = round_up32(V) < 64 ? 64 : round_up32(V);
-            silu_mul_quant_vec_kernel<1, 256><<<grid_rows(M), T, 0, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
-        } else if (V <= 1024) {
-            silu_mul_quant_vec_kernel<2, 512><<<grid_rows(M), round_up32((V + 1) / 2), 0, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
-        } else if (V <= 3072) {
-            silu_mul_quant_vec_kernel<4, 768><<<grid_rows(M), round_up32((V + 3) / 4), 0, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
-        } else {
-            silu_mul_quant_vec_kernel<8, 512><<<grid_rows(M), round_up32((V + 7) / 8), 0, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
+    const size_t row_smem = (size_t)N * sizeof(float);
+    if (vec && row_smem <= 200 * 1024) {
+        // the opt-in above 48 KB of dynamic shared memory is per device and per kernel
+        static bool opted_in[64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev < 0 || dev >= 64 || !opted_in[dev]) {
+            cudaFuncSetAttribute(silu_mul_quant_vec_kernel<128, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            cudaFuncSetAttribute(silu_mul_quant_vec_kernel<256, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            cudaFuncSetAttribute(silu_mul_quant_vec_kernel<384, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (dev >= 0 && dev < 64) opted_in[dev] = true;
         }
+        if (V <= 256)
+            silu_mul_quant_vec_kernel<128, 8><<<grid_rows(M), 128, row_smem, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
+        else if (V <= 1024)
+            silu_mul_quant_vec_kernel<256, 4><<<grid_rows(M), 256, row_smem, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
+        else
+            silu_mul_quant_vec_kernel<384, 3><<<grid_rows(M), 384, row_smem, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
     } else {
         silu_mul_quant_generic_kernel<<<grid_rows(M), 256, 0, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
     }

@@ -43,12 +43,26 @@ __device__ __forceinline__ void scale_from_amax(float amax, float& scale, float&
     inv = __fdiv_rn(127.0f, am);
 }
 
-// round-half-even(x*inv), clamped to [-128,127].  cvt.rni.s32 is rintf followed by an
-// exact conversion; |x*inv| <= 127*(1+2^-23) for finite inputs so the clamp never
-// changes a value that came from the same row's amax, but it is kept for safety.
+// round-half-even(x*inv), clamped to [-128,127]: the scalar form used by the generic
+// kernels.  cvt.rni.s32 is rintf followed by an exact conversion.
 __device__ __forceinline__ int quant_rn(float x, float inv) {
     int q = __float2int_rn(__fmul_rn(x, inv));
     return max(-128, min(127, q));
+}
+
+// The same code without a conversion instruction: t = x*inv (rounded), then t + 1.5*2^23
+// rounds t to the nearest-even integer and leaves it, in two's complement, in the low
+// mantissa bits, so the low byte of the sum's bit pattern IS the int8 code.  Valid while
+// |t| < 2^22; for a finite row |t| <= 127*(1+2^-22) because inv came from the row's own
+// amax, so the [-128,127] clamp of the scalar form can never bind and is dropped.  Rows
+// that contain Inf or NaN give unspecified codes (as they do in the reference).
+__device__ __forceinline__ uint32_t quant_rn_lowbyte(float x, float inv) {
+    return __float_as_uint(__fadd_rn(__fmul_rn(x, inv), 12582912.0f));
+}
+
+// low bytes of four words -> one word (a in byte 0)
+__device__ __forceinline__ uint32_t pack_lowbytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
 
 // group quantiser: true division by the stored scale, clamp, truncate toward zero
@@ -100,8 +114,47 @@ __device__ __forceinline__ float exp_fixed(float x) {
 // h = ((1/(1+exp(-g))) * g) * u, each step rounded to f32
 __device__ __forceinline__ float silu_mul(float g, float u) {
     float e = exp_fixed(-g);
-    float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, e));
+    float sig = __frcp_rn(__fadd_rn(1.0f, e));  // correctly rounded reciprocal == IEEE 1.0f / x
     return __fmul_rn(__fmul_rn(sig, g), u);
+}
+
+// ---- two-lane forms ------------------------------------------------------------------
+// The same operation sequences on float2 with the packed fma.rn.f32x2 / mul / add of
+// sm_100: each half is an independent, correctly rounded binary32 operation, so results
+// are bit-identical to the scalar forms while needing half the issue slots.
+__device__ __forceinline__ float2 splat2(float v) { return make_float2(v, v); }
+
+__device__ __forceinline__ float2 bf16x2_to_f32x2(uint32_t w) {
+    return make_float2(bf16lo_to_f32(w), bf16hi_to_f32(w));
+}
+
+__device__ __forceinline__ float2 exp_fixed2(float2 x) {
+    x.x = fminf(fmaxf(x.x, -kExpClamp), kExpClamp);
+    x.y = fminf(fmaxf(x.y, -kExpClamp), kExpClamp);
+    const float2 z = __ffma2_rn(x, splat2(kLog2e), splat2(kRoundMagic));
+    const float2 n = __fadd2_rn(z, splat2(-kRoundMagic));
+    float2 r = __ffma2_rn(n, splat2(-kLn2Hi), x);
+    r = __ffma2_rn(n, splat2(-kLn2Lo), r);
+    float2 p = __ffma2_rn(r, splat2(kExpC6), splat2(kExpC5));
+    p = __ffma2_rn(r, p, splat2(kExpC4));
+    p = __ffma2_rn(r, p, splat2(kExpC3));
+    p = __ffma2_rn(r, p, splat2(kExpC2));
+    p = __ffma2_rn(r, p, splat2(1.0f));
+    p = __ffma2_rn(r, p, splat2(1.0f));
+    return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(z.x) << 23)),
+                       __int_as_float(__float_as_int(p.y) + (__float_as_int(z.y) << 23)));
+}
+
+__device__ __forceinline__ float2 silu_mul2(float2 g, float2 u) {
+    const float2 e = exp_fixed2(make_float2(-g.x, -g.y));
+    const float2 d = __fadd2_rn(splat2(1.0f), e);
+    const float2 sig = make_float2(__frcp_rn(d.x), __frcp_rn(d.y));
+    return __fmul2_rn(__fmul2_rn(sig, g), u);
+}
+
+// int8 codes of two values in the low bytes of the two returned words (see quant_rn_lowbyte)
+__device__ __forceinline__ float2 quant_rn_lowbyte2(float2 x, float2 inv2) {
+    return __fadd2_rn(__fmul2_rn(x, inv2), splat2(kRoundMagic));
 }
 
 // rrms = 1 / sqrt(sumsq / n + eps)

@@ -70,6 +70,25 @@ def test_w8a8_gemm_matches_oracle(cabi, ext, m, n, k):
     _check_bf16(out3, ref, "alias")
 
 
+@pytest.mark.parametrize("m,n,k", [(1100, 2320, 272), (2048, 4096, 128), (1537, 4104, 400), (4096, 2560, 7168)])
+def test_gemm_cta_pair_kernel(cabi, m, n, k):
+    # large enough for the 256 x 256 CTA-pair kernel; ragged last tiles in M and N, short and long K
+    A, B, sa, sb = _operands(m, n, k, seed=m + n + k)
+    Ad, Bd = A.cuda(), B.cuda()
+    acc = cabi.w8a8_gemm_i32(Ad, Bd)
+    out = cabi.w8a8_gemm(Ad, Bd, sa.cuda(), sb.cuda())
+    assert cabi.device_status() == 0
+    if m * n * k <= 2e10:
+        ref_acc = oracle.gemm_i32(A, B)
+        assert (acc.cpu() != ref_acc).sum().item() == 0
+        _check_bf16(out, oracle.w8a8_gemm(A, B, sa, sb), "pair kernel")
+    else:
+        rows = torch.arange(0, m, 37)
+        ref_acc = oracle.gemm_i32(A[rows], B)
+        assert (acc.cpu()[rows] != ref_acc).sum().item() == 0
+        _check_bf16(out[rows.cuda()], oracle.scale_convert(ref_acc, sa[rows], sb), "pair kernel (sampled rows)")
+
+
 def test_gemm_many_tiles_per_cta(cabi):
     # 2048 x 4096 -> 256 tiles of 128x256 on 148 CTAs: every CTA loops, both accumulators cycle
     m, n, k = 2048, 4096, 1024
