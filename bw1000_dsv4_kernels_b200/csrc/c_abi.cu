@@ -86,7 +86,7 @@ int launch_add_rmsnorm_quant(void* res, const void* x, const void* w, void* q, v
 }
 
 int launch_silu_mul_quant_strided(const void* g, int64_t ldg, const void* u, int64_t ldu, const int* mask,
-                                  void* q, void* s, int M, int N, dsv4_stream_t stream) {
+                                  const int* valid_rows, void* q, void* s, int M, int N, dsv4_stream_t stream) {
     if (int rc = check_rows("silu_mul_quant", M, N)) return rc;
     if (M == 0 || N == 0) return 0;
     DSV4_REQUIRE_PTR("silu_mul_quant", g);
@@ -94,16 +94,16 @@ int launch_silu_mul_quant_strided(const void* g, int64_t ldg, const void* u, int
     DSV4_REQUIRE_PTR("silu_mul_quant", q);
     DSV4_REQUIRE_PTR("silu_mul_quant", s);
     if (ldg < N || ldu < N) return fail(DSV4_ERR_ARG, "silu_mul_quant: row stride smaller than N");
-    return silu_mul_quant(g, u, mask, q, s, M, N, ldg, ldu, cs(stream));
+    return silu_mul_quant(g, u, mask, valid_rows, q, s, M, N, ldg, ldu, cs(stream));
 }
 
 int launch_silu_mul_quant(const void* g, const void* u, void* q, void* s, int M, int N, dsv4_stream_t stream) {
-    return launch_silu_mul_quant_strided(g, N, u, N, nullptr, q, s, M, N, stream);
+    return launch_silu_mul_quant_strided(g, N, u, N, nullptr, nullptr, q, s, M, N, stream);
 }
 
 int launch_silu_mul_masked_quant(const void* g, const void* u, const int* mask, void* q, void* s, int M, int N,
                                  dsv4_stream_t stream) {
-    return launch_silu_mul_quant_strided(g, N, u, N, mask, q, s, M, N, stream);
+    return launch_silu_mul_quant_strided(g, N, u, N, mask, nullptr, q, s, M, N, stream);
 }
 
 int launch_rmsnorm(void* x, int M, int N, float eps, dsv4_stream_t stream) {
@@ -166,14 +166,29 @@ int launch_grouped_gemm(const void* A, const void* W, const void* sa, const void
     return gemm_i8(a, cs(stream));
 }
 
-int launch_moe_segments(const int* topk_ids, int T, int topk, int E, int* expert_offsets, int* src_row,
-                        int* dst_slot, dsv4_stream_t stream) {
-    return moe_segments(topk_ids, T, topk, E, expert_offsets, src_row, dst_slot, cs(stream));
+int launch_moe_segments(const int* topk_ids, int T, int topk, int E, int expert_lo, int* expert_offsets,
+                        int* src_row, int* dst_slot, dsv4_stream_t stream) {
+    if (expert_lo < 0) return fail(DSV4_ERR_ARG, "moe_segments: expert_lo must not be negative");
+    return moe_segments(topk_ids, T, topk, E, expert_lo, expert_offsets, src_row, dst_slot, cs(stream));
 }
 
 int launch_gather_rows(const void* src, const int* src_row, void* dst, int R, int row_bytes,
-                       const float* src_scale, float* dst_scale, int scales_per_row, dsv4_stream_t stream) {
-    return gather_rows(src, src_row, dst, R, row_bytes, src_scale, dst_scale, scales_per_row, cs(stream));
+                       const float* src_scale, float* dst_scale, int scales_per_row, const int* valid_rows,
+                       dsv4_stream_t stream) {
+    return gather_rows(src, src_row, dst, R, row_bytes, src_scale, dst_scale, scales_per_row, valid_rows, cs(stream));
+}
+
+int launch_moe_combine(const void* z, const int* dst_slot, const float* topk_w, void* out, int T, int topk, int H,
+                       int out_f32, dsv4_stream_t stream) {
+    return moe_combine(z, dst_slot, topk_w, out, T, topk, H, out_f32, cs(stream));
+}
+
+int launch_w8a8_gemm_ld(const void* A, const void* B, const void* sa, const void* sb, void* C, int64_t ldc, int M,
+                        int N, int K, dsv4_stream_t stream) {
+    GemmArgs a{};
+    a.A = A; a.B = B; a.sa = static_cast<const float*>(sa); a.sb = static_cast<const float*>(sb); a.C = C;
+    a.offsets = nullptr; a.M = M; a.N = N; a.K = K; a.E = 1; a.ldc = ldc; a.sa_groups = 1; a.out_i32 = 0;
+    return gemm_i8(a, cs(stream));
 }
 
 }  // extern "C"

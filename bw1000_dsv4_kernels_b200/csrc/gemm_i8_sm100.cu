@@ -578,6 +578,459 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
 }
 
+
+// ------------------------------------------------------------------------------------
+// Group-scaled kernel (grouped or dense): the activation scale changes every 128 columns
+// of K, so each 128-deep K block is its own int32 accumulator.  The MMA warp alternates
+// between two 128-column accumulators in tensor memory; the drain warps fold block g into
+// fp32 registers as y = fma(float(acc_g), sa[row, g], y) while the MMAs of block g+1 run,
+// and apply the channel scale once at the end of the tile.  Tile = 128 x 128.
+// ------------------------------------------------------------------------------------
+constexpr int GSN = 128;
+
+template <int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const Params p) {
+    using L = Smem<GSN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float* sb_tile = reinterpret_cast<float*>(smem + L::kSbOff);
+    int* prefix = reinterpret_cast<int*>(smem + L::kPrefixOff);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ((L::kBarOff + 7) & ~7));
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlotOff);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
+
+    const uint32_t tiles_base = ptx::smem_u32(smem);
+    const uint32_t bar_base = ptx::smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto blk_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto blk_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr uint32_t kTmemCols = 2 * GSN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(blk_full_bar(a), 1);
+            ptx::mbar_init(blk_empty_bar(a), kDrainThreads / 32);
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+        ptx::prefetch_tensormap(&tmA);
+        ptx::prefetch_tensormap(&tmB);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    if (p.offsets != nullptr && warp == 2) {
+        int carry = 0;
+        for (int e0 = 0; e0 < p.E; e0 += 32) {
+            const int e = e0 + lane;
+            int cnt = 0;
+            if (e < p.E) cnt = (p.offsets[e + 1] - p.offsets[e] + BM - 1) / BM;
+            int incl = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            if (e < p.E) prefix[e] = carry + incl - cnt;
+            carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) prefix[p.E] = carry;
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const Scheduler sched(p, prefix, GSN);
+    const int k_blocks = (p.K + BK - 1) / BK;
+
+    if (warp == 0) {
+        if (ptx::elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
+                const TileCoord c = sched.at(t, GSN);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u) || *abort_flag) {
+                        report_wait_failure(kWaitEmptyStage);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = tiles_base + stage * L::kStageBytes;
+                    ptx::mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
+                    ptx::tma_load_2d(a_dst, &tmA, kb * BK, c.a_row0, full_bar(stage));
+                    ptx::tma_load_2d(a_dst + L::kABytes, &tmB, kb * BK, c.b_row0, full_bar(stage));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (ptx::elect_one()) {
+            constexpr uint32_t idesc = ptx::idesc_i8(BM, GSN);
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t blk = 0;  // running K-block counter: buffer = blk & 1, parity = (blk >> 1) & 1
+            bool ok = true;
+            for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
+                for (int kb = 0; kb < k_blocks; ++kb, ++blk) {
+                    const int b = blk & 1;
+                    if (!ptx::mbar_wait_bounded(blk_empty_bar(b), ((blk >> 1) & 1u) ^ 1u) ||
+                        !ptx::mbar_wait_bounded(full_bar(stage), phase) || *abort_flag) {
+                        report_wait_failure(kWaitFullStage);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_src = tiles_base + stage * L::kStageBytes;
+                    const uint64_t adesc = ptx::smem_desc_k_sw128(a_src);
+                    const uint64_t bdesc = ptx::smem_desc_k_sw128(a_src + L::kABytes);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        ptx::mma_i8_ss(tmem_base + b * GSN, adesc + 2u * k, bdesc + 2u * k, idesc, k != 0 ? 1u : 0u);
+                    ptx::tc_commit(empty_bar(stage));
+                    ptx::tc_commit(blk_full_bar(b));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        float* sbs = sb_tile + (warp - 2) * GSN;
+        const bool vec_ok = c_vector_stores_ok(p);
+        uint32_t blk = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
+            const TileCoord c = sched.at(t, GSN);
+            __syncwarp();
+            {
+                const float* sb_row = p.sb + (int64_t)c.expert * p.N;
+                for (int j = lane; j < GSN; j += 32) sbs[j] = (c.n0 + j < p.N) ? __ldg(sb_row + c.n0 + j) : 0.0f;
+            }
+            __syncwarp();
+            const int row = c.a_row0 + quarter * 32 + lane;
+            const bool row_ok = row < c.row_end;
+            const float* sa_row = p.sa + (int64_t)(row_ok ? row : 0) * p.sa_groups;
+            float y[GSN];
+#pragma unroll
+            for (int j = 0; j < GSN; ++j) y[j] = 0.0f;
+            for (int kb = 0; kb < k_blocks; ++kb, ++blk) {
+                const int b = blk & 1;
+                const float sg = row_ok ? __ldg(sa_row + kb) : 0.0f;
+                if (!ptx::mbar_wait_bounded(blk_full_bar(b), (blk >> 1) & 1u) || *abort_flag) {
+                    report_wait_failure(kWaitAccFull);
+                    *abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                __syncwarp();  // tcgen05.ld is warp-collective
+                const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + b * GSN;
+#pragma unroll
+                for (int cc = 0; cc < GSN / 32; ++cc) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32b_x32(t_lane + cc * 32, r);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        y[cc * 32 + j] = __fmaf_rn(__int2float_rn((int)r[j]), sg, y[cc * 32 + j]);
+                }
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(blk_empty_bar(b));
+            }
+            if (!ok) break;
+            if (row_ok) {
+                __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.C) + (int64_t)row * p.ldc + c.n0;
+#pragma unroll
+                for (int j8 = 0; j8 < GSN / 8; ++j8) {
+                    const int n = c.n0 + j8 * 8;
+                    if (n >= p.N) break;
+                    const float4 s0 = *reinterpret_cast<const float4*>(sbs + j8 * 8);
+                    const float4 s1 = *reinterpret_cast<const float4*>(sbs + j8 * 8 + 4);
+                    uint4 o;
+                    o.x = pack_bf16x2_rn(__fmul_rn(y[j8 * 8 + 0], s0.x), __fmul_rn(y[j8 * 8 + 1], s0.y));
+                    o.y = pack_bf16x2_rn(__fmul_rn(y[j8 * 8 + 2], s0.z), __fmul_rn(y[j8 * 8 + 3], s0.w));
+                    o.z = pack_bf16x2_rn(__fmul_rn(y[j8 * 8 + 4], s1.x), __fmul_rn(y[j8 * 8 + 5], s1.y));
+                    o.w = pack_bf16x2_rn(__fmul_rn(y[j8 * 8 + 6], s1.z), __fmul_rn(y[j8 * 8 + 7], s1.w));
+                    if (vec_ok && n + 8 <= p.N) {
+                        *reinterpret_cast<uint4*>(out + j8 * 8) = o;
+                    } else {
+                        const uint32_t w4[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (n + j < p.N)
+                                reinterpret_cast<uint16_t*>(out)[j8 * 8 + j] =
+                                    (j & 1) ? (uint16_t)(w4[j >> 1] >> 16) : (uint16_t)(w4[j >> 1] & 0xffffu);
+                    }
+                }
+            }
+        }
+    }
+
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+
+// ------------------------------------------------------------------------------------
+// Weight-streaming kernel for few tokens (M <= 256): HBM-bound on the weight read, so the
+// operands are swapped and K is split.
+//   * The 128 weight rows of a tile sit on the MMA's M axis (TMEM lanes), the tokens on its
+//     N axis (NTOK columns, 16..256), so no tensor-core rows are spent on padding and the
+//     whole weight is read exactly once whatever M is.
+//   * A cluster of S CTAs shares one 128-row weight tile and splits K between its CTAs, so
+//     that ~all SMs stream weights at once.  Each CTA parks its int32 partial [NTOK][128] in
+//     its own shared memory (on top of the drained stage ring); after a cluster barrier CTA s
+//     sums the S partials of its share of the token columns through distributed shared memory
+//     (exact int32 adds, fixed order), applies the scales and stores.  No scratch in HBM.
+// One tile per CTA: not persistent.
+// ------------------------------------------------------------------------------------
+template <int NTOK>
+struct StreamSmem {
+    static constexpr int kWBytes = 128 * BK;
+    static constexpr int kXBytes = NTOK * BK;
+    static constexpr int kStageBytes = kWBytes + kXBytes;
+    static constexpr int kBudget = 196 * 1024;
+    static constexpr int kStages = kBudget / kStageBytes;
+    static constexpr int kTilesBytes = kStages * kStageBytes;
+    static constexpr int kPartialBytes = NTOK * 128 * 4;
+    static_assert(kPartialBytes <= kTilesBytes, "the partial tile reuses the stage ring");
+    static constexpr int kBarOff = kTilesBytes;
+    static constexpr int kNumBars = 2 * kStages + 1;
+    static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
+    static constexpr int kAbortOff = kTmemSlotOff + 4;
+    static constexpr int kTotal = kAbortOff + 4;
+    static constexpr int kDynamic = kTotal + 1024;
+};
+
+template <int NTOK>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_i8_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                      const Params p) {
+    using L = StreamSmem<NTOK>;
+    constexpr int STAGES = L::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlotOff);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
+    int* partial = reinterpret_cast<int*>(smem);  // [NTOK][128] once the ring has drained
+
+    const uint32_t tiles_base = ptx::smem_u32(smem);
+    const uint32_t bar_base = ptx::smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    const uint32_t acc_full_bar = bar_base + 8u * (2 * STAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int S = (int)ptx::cluster_nctarank();
+    const int split = (int)ptx::cluster_ctarank();
+    const int nt = blockIdx.x / S;
+    const int n0 = nt * 128;
+    constexpr uint32_t kTmemCols = NTOK < 32 ? 32 : NTOK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        ptx::mbar_init(acc_full_bar, 1);
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+        ptx::prefetch_tensormap(&tmW);
+        ptx::prefetch_tensormap(&tmX);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // this CTA's share of the K blocks
+    const int k_blocks = (p.K + BK - 1) / BK;
+    const int kb0 = (int)((int64_t)k_blocks * split / S), kb1 = (int)((int64_t)k_blocks * (split + 1) / S);
+    bool ok = true;
+
+    if (warp == 0) {
+        if (ptx::elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u) || *abort_flag) {
+                    report_wait_failure(kWaitEmptyStage);
+                    *abort_flag = 1;
+                    break;
+                }
+                const uint32_t w_dst = tiles_base + stage * L::kStageBytes;
+                ptx::mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
+                ptx::tma_load_2d(w_dst, &tmW, kb * BK, n0, full_bar(stage));
+                ptx::tma_load_2d(w_dst + L::kWBytes, &tmX, kb * BK, 0, full_bar(stage));
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        if (ptx::elect_one()) {
+            constexpr uint32_t idesc = ptx::idesc_i8(128, NTOK);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool issued_all = true;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                if (!ptx::mbar_wait_bounded(full_bar(stage), phase) || *abort_flag) {
+                    report_wait_failure(kWaitFullStage);
+                    *abort_flag = 1;
+                    issued_all = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t w_src = tiles_base + stage * L::kStageBytes;
+                const uint64_t adesc = ptx::smem_desc_k_sw128(w_src);
+                const uint64_t bdesc = ptx::smem_desc_k_sw128(w_src + L::kWBytes);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    ptx::mma_i8_ss(tmem_base, adesc + 2u * k, bdesc + 2u * k, idesc, (kb > kb0 || k != 0) ? 1u : 0u);
+                ptx::tc_commit(empty_bar(stage));
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+            if (issued_all) ptx::tc_commit(acc_full_bar);
+        }
+    } else {
+        // drain warps: accumulator -> shared partial (or straight out when K is not split)
+        const int quarter = warp & 3;
+        const int wrow = quarter * 32 + lane;  // weight row inside the tile = TMEM lane
+        if (kb1 > kb0) {
+            if (!ptx::mbar_wait_bounded(acc_full_bar, 0) || *abort_flag) {
+                report_wait_failure(kWaitAccFull);
+                *abort_flag = 1;
+                ok = false;
+            }
+        }
+        ptx::tc_fence_after_sync();
+        __syncwarp();
+        if (ok) {
+            const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+            for (int cc = 0; cc < (NTOK + 31) / 32; ++cc) {
+                uint32_t r[32];
+                if (kb1 > kb0) {
+                    if (NTOK >= 32) {
+                        ptx::tmem_ld_32x32b_x32(t_lane + cc * 32, r);
+                    } else {
+                        uint32_t r16[16];
+                        ptx::tmem_ld_32x32b_x16(t_lane, r16);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) r[j] = r16[j];
+#pragma unroll
+                        for (int j = 16; j < 32; ++j) r[j] = 0;
+                    }
+                    ptx::tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = 0;  // a CTA without K blocks contributes zero
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (cc * 32 + j < NTOK) partial[(cc * 32 + j) * 128 + wrow] = (int)r[j];
+            }
+        }
+    }
+
+    // every CTA's partial is complete and visible to the cluster
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();
+
+    if (warp >= 2) {
+        // Work item = (token column c, group of four weight rows): 16-byte loads of the S partials,
+        // four sums, four outputs that are contiguous in C.  Consecutive threads take consecutive
+        // row groups of one column.
+        const int tid = threadIdx.x - 64;
+        const int cols_lo = (int)((int64_t)NTOK * split / S);
+        int cols_hi = (int)((int64_t)NTOK * (split + 1) / S);
+        if (cols_hi > p.M) cols_hi = p.M;
+        const uint32_t my_partial = ptx::smem_u32(partial);
+        uint32_t peer_base[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) peer_base[r] = ptx::map_to_cta(my_partial, r < S ? r : 0);
+        const bool vec_store = p.out_i32 ? ((p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0))
+                                         : ((p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 7) == 0));
+        const int items = (cols_hi - cols_lo) * 32;
+        for (int it = tid; it < items; it += kDrainThreads) {
+            const int c = cols_lo + (it >> 5), g = it & 31;
+            const uint32_t off = (uint32_t)(c * 128 + g * 4) * 4u;
+            int a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                if (r < S) {
+                    const uint4 v = ptx::ld_shared_cluster_v4(peer_base[r] + off);
+                    a0 += (int)v.x; a1 += (int)v.y; a2 += (int)v.z; a3 += (int)v.w;
+                }
+            }
+            const int n = n0 + g * 4;
+            if (n >= p.N) continue;
+            if (p.out_i32) {
+                int* out = static_cast<int*>(p.C) + (int64_t)c * p.ldc + n;
+                if (vec_store && n + 4 <= p.N) {
+                    *reinterpret_cast<int4*>(out) = make_int4(a0, a1, a2, a3);
+                } else {
+                    const int v4[4] = {a0, a1, a2, a3};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (n + j < p.N) out[j] = v4[j];
+                }
+            } else {
+                const float sa = __ldg(p.sa + c);
+                float sbv[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sbv[j] = (n + j < p.N) ? __ldg(p.sb + n + j) : 0.0f;
+                const uint32_t lo = pack_bf16x2_rn(__fmul_rn(__fmul_rn(__int2float_rn(a0), sa), sbv[0]),
+                                                   __fmul_rn(__fmul_rn(__int2float_rn(a1), sa), sbv[1]));
+                const uint32_t hi = pack_bf16x2_rn(__fmul_rn(__fmul_rn(__int2float_rn(a2), sa), sbv[2]),
+                                                   __fmul_rn(__fmul_rn(__int2float_rn(a3), sa), sbv[3]));
+                __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.C) + (int64_t)c * p.ldc + n;
+                if (vec_store && n + 4 <= p.N) {
+                    *reinterpret_cast<uint2*>(out) = make_uint2(lo, hi);
+                } else {
+                    const uint16_t h4[4] = {(uint16_t)(lo & 0xffffu), (uint16_t)(lo >> 16), (uint16_t)(hi & 0xffffu),
+                                            (uint16_t)(hi >> 16)};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (n + j < p.N) reinterpret_cast<uint16_t*>(out)[j] = h4[j];
+                }
+            }
+        }
+    }
+
+    // nobody leaves while a peer may still read its shared memory
+    __syncthreads();
+    ptx::cluster_sync();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
 // ------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------
@@ -654,6 +1107,63 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params&
     return check_launch("w8a8_gemm");
 }
 
+template <int NTOK>
+int launch_stream_variant(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, int n_tiles, int splits,
+                          cudaStream_t st) {
+    using L = StreamSmem<NTOK>;
+    static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
+    static bool opted_in[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !opted_in[dev]) {
+        if (cudaFuncSetAttribute(gemm_i8_stream_kernel<NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 L::kDynamic) != cudaSuccess)
+            return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: cannot raise the dynamic shared memory limit");
+        if (dev >= 0 && dev < 64) opted_in[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(n_tiles * splits), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = L::kDynamic;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_i8_stream_kernel<NTOK>, tmW, tmX, p);
+    if (err != cudaSuccess) {
+        cudaGetLastError();  // clear the sticky launch error
+        static thread_local char msg[160];
+        snprintf(msg, sizeof msg, "w8a8_gemm (weight streaming): %s", cudaGetErrorString(err));
+        return fail(DSV4_ERR_LAUNCH, msg);
+    }
+    return check_launch("w8a8_gemm (weight streaming)");
+}
+
+template <int STAGES>
+int launch_gs_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, int max_tiles, cudaStream_t st) {
+    using L = Smem<GSN, STAGES>;
+    static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
+    static bool opted_in[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !opted_in[dev]) {
+        if (cudaFuncSetAttribute(gemm_i8_gs_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 L::kDynamic) != cudaSuccess)
+            return fail(DSV4_ERR_LAUNCH, "grouped_gemm: cannot raise the dynamic shared memory limit");
+        if (dev >= 0 && dev < 64) opted_in[dev] = true;
+    }
+    int grid = sm_count();
+    if (grid <= 0) return fail(DSV4_ERR_LAUNCH, "grouped_gemm: no CUDA device");
+    if (max_tiles < grid) grid = max_tiles;
+    if (grid < 1) grid = 1;
+    gemm_i8_gs_kernel<STAGES><<<grid, kThreads, L::kDynamic, st>>>(tmA, tmB, p);
+    return check_launch("grouped_gemm (group-scaled)");
+}
+
 template <int STAGES>
 int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, cudaStream_t st) {
     using L = PairSmem<STAGES>;
@@ -688,7 +1198,11 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
     if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15))
         return fail(DSV4_ERR_ARG, "w8a8_gemm: A and B must be 16-byte aligned");
     if (grouped && (a.E <= 0 || a.E > kMaxExperts)) return fail(DSV4_ERR_ARG, "grouped_gemm: E must be in 1..1024");
-    if (a.sa_groups != 1) return fail(DSV4_ERR_ARG, "grouped_gemm: this build supports per-token scales only");
+    if (a.sa_groups != 1) {
+        if (a.out_i32) return fail(DSV4_ERR_ARG, "w8a8_gemm: raw accumulators exist only for per-token scaling");
+        if (a.K % 128 != 0 || a.sa_groups != a.K / 128)
+            return fail(DSV4_ERR_ARG, "grouped_gemm: group scales need K % 128 == 0 and sa_groups == K / 128");
+    }
 
     Params p;
     p.sa = a.sa; p.sb = a.sb; p.C = a.C; p.offsets = a.offsets;
@@ -709,6 +1223,34 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
     if (bn == 64 && (int64_t)tiles_m_bound * ((a.N + 63) / 64) < sms) bn = 32;
 
     CUtensorMap tmA, tmB;
+    if (a.sa_groups != 1) {
+        int rc3 = make_tile_map(&tmA, a.A, (uint64_t)a.M, (uint64_t)a.K, BM);
+        if (rc3) return rc3;
+        rc3 = make_tile_map(&tmB, a.B, b_rows, (uint64_t)a.K, GSN);
+        if (rc3) return rc3;
+        return launch_gs_variant<6>(tmA, tmB, p, tiles_m_bound * ((a.N + GSN - 1) / GSN), st);
+    }
+    // Few tokens: stream the weight once, tokens on the MMA's N axis, K split over a cluster
+    if (!grouped && a.M <= 256) {
+        const int n_tiles = (a.N + 127) / 128;
+        const int k_blocks = (a.K + BK - 1) / BK;
+        int splits = sms / n_tiles;
+        if (splits > 8) splits = 8;
+        if (splits > k_blocks) splits = k_blocks;
+        if (splits < 1) splits = 1;
+        const int ntok = a.M <= 16 ? 16 : a.M <= 32 ? 32 : a.M <= 64 ? 64 : a.M <= 128 ? 128 : 256;
+        int rc4 = make_tile_map(&tmA, a.B, b_rows, (uint64_t)a.K, 128);   // weights
+        if (rc4) return rc4;
+        rc4 = make_tile_map(&tmB, a.A, (uint64_t)a.M, (uint64_t)a.K, (uint32_t)ntok);  // tokens
+        if (rc4) return rc4;
+        switch (ntok) {
+            case 16: return launch_stream_variant<16>(tmA, tmB, p, n_tiles, splits, st);
+            case 32: return launch_stream_variant<32>(tmA, tmB, p, n_tiles, splits, st);
+            case 64: return launch_stream_variant<64>(tmA, tmB, p, n_tiles, splits, st);
+            case 128: return launch_stream_variant<128>(tmA, tmB, p, n_tiles, splits, st);
+            default: return launch_stream_variant<256>(tmA, tmB, p, n_tiles, splits, st);
+        }
+    }
     // Dense problems with more than one 128-row tile go to the CTA-pair kernel
     if (!grouped && a.M > 128 && (int64_t)((a.M + 255) / 256) * ((a.N + 255) / 256) >= sms / 4) {
         int rc2 = make_tile_map(&tmA, a.A, (uint64_t)a.M, (uint64_t)a.K, BM);

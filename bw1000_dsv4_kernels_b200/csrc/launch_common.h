@@ -18,8 +18,8 @@ int ptgq(const void* x, void* q, void* s, int M, int K, int gs, cudaStream_t st)
 int add_rmsnorm_quant(void* res, const void* x, const void* w, void* q, void* s, int M, int K,
                       float eps, cudaStream_t st);
 int rmsnorm(void* x, int M, int K, float eps, cudaStream_t st);
-int silu_mul_quant(const void* g, const void* u, const int* mask, void* q, void* s, int M, int N,
-                   int64_t ldg, int64_t ldu, cudaStream_t st);
+int silu_mul_quant(const void* g, const void* u, const int* mask, const int* valid_rows, void* q, void* s,
+                   int M, int N, int64_t ldg, int64_t ldu, cudaStream_t st);
 int silu_mul(const void* g, const void* u, void* out, int M, int N, int64_t ldg, int64_t ldu,
              cudaStream_t st);
 
@@ -41,10 +41,13 @@ int scale_convert(const void* acc, const void* sa, const void* sb, void* out, in
                   cudaStream_t st);
 
 // ---- launchers implemented in moe_segments.cu -------------------------------------
-int moe_segments(const int* topk_ids, int T, int topk, int E, int* offsets, int* src_row,
+int moe_segments(const int* topk_ids, int T, int topk, int E, int expert_lo, int* offsets, int* src_row,
                  int* dst_slot, cudaStream_t st);
 int gather_rows(const void* src, const int* src_row, void* dst, int R, int row_bytes,
-                const float* src_scale, float* dst_scale, int scales_per_row, cudaStream_t st);
+                const float* src_scale, float* dst_scale, int scales_per_row, const int* valid_rows,
+                cudaStream_t st);
+int moe_combine(const void* z, const int* dst_slot, const float* w, void* out, int T, int topk, int H,
+                int out_f32, cudaStream_t st);
 int read_device_status(cudaStream_t st, int* out);
 
 }  // namespace w8a8

@@ -1,6 +1,8 @@
 // Expert segments for the MoE grouped GEMM, computed on the device from top-k routing
 // ids: a stable counting sort by expert, written without atomics and without scratch
 // memory so that the row order inside an expert is reproducible (increasing (token, slot)).
+// With expert_lo > 0 only experts [expert_lo, expert_lo + E) are sorted (expert parallelism);
+// pairs routed elsewhere get slot -1.
 //
 //   count   : CTA e counts the pairs routed to expert e        -> offsets[e+1] = count
 //   scan    : one warp turns the counts into exclusive offsets -> offsets[0..E]
@@ -9,6 +11,7 @@
 //
 // The id list (T*topk int32, 128 KB at 4096 tokens x 8) stays in L2 across the E CTAs.
 #include <cuda_runtime.h>
+#include <cuda_bf16.h>
 #include <cstdint>
 
 #include "launch_common.h"
@@ -28,9 +31,12 @@ __device__ __forceinline__ int warp_incl_scan(int v, int lane) {
 }
 
 __global__ void __launch_bounds__(kSegThreads) seg_count_kernel(const int* __restrict__ ids, int R,
-                                                                int* __restrict__ offsets) {
+                                                                int expert_lo, int* __restrict__ offsets,
+                                                                int* __restrict__ dst_slot) {
     __shared__ int red[kSegThreads / 32];
-    const int e = blockIdx.x;
+    const int e = blockIdx.x + expert_lo;
+    // pairs routed to experts outside [expert_lo, expert_lo + E) keep slot -1
+    for (int i = blockIdx.x * kSegThreads + threadIdx.x; i < R; i += gridDim.x * kSegThreads) dst_slot[i] = -1;
     int c = 0;
     for (int i = threadIdx.x; i < R; i += kSegThreads) c += (__ldg(ids + i) == e);
 #pragma unroll
@@ -40,7 +46,7 @@ __global__ void __launch_bounds__(kSegThreads) seg_count_kernel(const int* __res
     if (threadIdx.x == 0) {
         int t = 0;
         for (int w = 0; w < kSegThreads / 32; ++w) t += red[w];
-        offsets[e + 1] = t;
+        offsets[blockIdx.x + 1] = t;
     }
 }
 
@@ -59,14 +65,14 @@ __global__ void __launch_bounds__(32) seg_scan_kernel(int* __restrict__ offsets,
 }
 
 __global__ void __launch_bounds__(kSegThreads) seg_scatter_kernel(const int* __restrict__ ids, int R,
-                                                                  int topk,
+                                                                  int topk, int expert_lo,
                                                                   const int* __restrict__ offsets,
                                                                   int* __restrict__ src_row,
                                                                   int* __restrict__ dst_slot) {
     __shared__ int warp_tot[kSegThreads / 32];
-    const int e = blockIdx.x;
+    const int e = blockIdx.x + expert_lo;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    int base = offsets[e];
+    int base = offsets[blockIdx.x];
     for (int i0 = 0; i0 < R; i0 += kSegThreads) {
         const int i = i0 + threadIdx.x;
         const bool hit = (i < R) && (__ldg(ids + i) == e);
@@ -95,7 +101,9 @@ __global__ void __launch_bounds__(128) gather_rows_kernel(const uint4* __restric
                                                           const int* __restrict__ src_row,
                                                           uint4* __restrict__ dst, int R, int vec_per_row,
                                                           const float* __restrict__ src_scale,
-                                                          float* __restrict__ dst_scale, int spr) {
+                                                          float* __restrict__ dst_scale, int spr,
+                                                          const int* __restrict__ valid_rows) {
+    if (valid_rows != nullptr) R = min(R, __ldg(valid_rows));
     for (int r = blockIdx.x; r < R; r += gridDim.x) {
         const int t = __ldg(src_row + r);
         const uint4* s = src + (int64_t)t * vec_per_row;
@@ -107,31 +115,85 @@ __global__ void __launch_bounds__(128) gather_rows_kernel(const uint4* __restric
     }
 }
 
+// out[t, :] = sum over the token's top-k slots j (in order) of w[t,j] * Z[dst_slot[t,j], :],
+// accumulated in fp32 with fma; slots equal to -1 (expert not on this rank) are skipped.
+template <bool OUT_F32>
+__global__ void __launch_bounds__(128) moe_combine_kernel(const __nv_bfloat16* __restrict__ z,
+                                                          const int* __restrict__ dst_slot,
+                                                          const float* __restrict__ w, void* __restrict__ out, int T,
+                                                          int topk, int H) {
+    const int V = H >> 3;
+    for (int t = blockIdx.x; t < T; t += gridDim.x) {
+        for (int v = threadIdx.x; v < V; v += blockDim.x) {
+            float acc[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+            for (int j = 0; j < topk; ++j) {
+                const int slot = __ldg(dst_slot + (int64_t)t * topk + j);
+                if (slot < 0) continue;
+                const float wj = __ldg(w + (int64_t)t * topk + j);
+                const uint4 zv = __ldg(reinterpret_cast<const uint4*>(z + (int64_t)slot * H) + v);
+                const uint32_t zw[4] = {zv.x, zv.y, zv.z, zv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    acc[2 * e] = __fmaf_rn(wj, __uint_as_float(zw[e] << 16), acc[2 * e]);
+                    acc[2 * e + 1] = __fmaf_rn(wj, __uint_as_float(zw[e] & 0xffff0000u), acc[2 * e + 1]);
+                }
+            }
+            if (OUT_F32) {
+                float4* o = reinterpret_cast<float4*>(static_cast<float*>(out) + (int64_t)t * H) + 2 * v;
+                o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            } else {
+                __nv_bfloat162 b[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) b[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+                reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(out) + (int64_t)t * H)[v] =
+                    *reinterpret_cast<uint4*>(b);
+            }
+        }
+    }
+}
+
 }  // namespace
 
-int moe_segments(const int* topk_ids, int T, int topk, int E, int* offsets, int* src_row, int* dst_slot,
-                 cudaStream_t st) {
+int moe_combine(const void* z, const int* dst_slot, const float* w, void* out, int T, int topk, int H, int out_f32,
+                cudaStream_t st) {
+    if (T == 0 || H == 0) return 0;
+    if (T < 0 || topk <= 0 || H < 0 || H % 8 != 0) return fail(DSV4_ERR_ARG, "moe_combine: H must be a multiple of 8");
+    if (z == nullptr || dst_slot == nullptr || w == nullptr || out == nullptr) return fail(DSV4_ERR_ARG, "moe_combine: null pointer");
+    if ((reinterpret_cast<uintptr_t>(z) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+        return fail(DSV4_ERR_ARG, "moe_combine: z and out must be 16-byte aligned");
+    if (out_f32)
+        moe_combine_kernel<true><<<T, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(z), dst_slot, w, out, T, topk, H);
+    else
+        moe_combine_kernel<false><<<T, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(z), dst_slot, w, out, T, topk, H);
+    return check_launch("moe_combine");
+}
+
+int moe_segments(const int* topk_ids, int T, int topk, int E, int expert_lo, int* offsets, int* src_row,
+                 int* dst_slot, cudaStream_t st) {
     if (T < 0 || topk <= 0 || E <= 0) return fail(DSV4_ERR_ARG, "moe_segments: bad sizes");
     if (topk_ids == nullptr || offsets == nullptr || src_row == nullptr || dst_slot == nullptr)
         return fail(DSV4_ERR_ARG, "moe_segments: null pointer");
     const int64_t R64 = (int64_t)T * topk;
     if (R64 > INT32_MAX) return fail(DSV4_ERR_ARG, "moe_segments: T*topk exceeds int32");
     const int R = (int)R64;
-    seg_count_kernel<<<E, kSegThreads, 0, st>>>(topk_ids, R, offsets);
+    seg_count_kernel<<<E, kSegThreads, 0, st>>>(topk_ids, R, expert_lo, offsets, dst_slot);
     seg_scan_kernel<<<1, 32, 0, st>>>(offsets, E);
-    seg_scatter_kernel<<<E, kSegThreads, 0, st>>>(topk_ids, R, topk, offsets, src_row, dst_slot);
+    seg_scatter_kernel<<<E, kSegThreads, 0, st>>>(topk_ids, R, topk, expert_lo, offsets, src_row, dst_slot);
     return check_launch("moe_segments");
 }
 
 int gather_rows(const void* src, const int* src_row, void* dst, int R, int row_bytes, const float* src_scale,
-                float* dst_scale, int scales_per_row, cudaStream_t st) {
+                float* dst_scale, int scales_per_row, const int* valid_rows, cudaStream_t st) {
     if (R == 0) return 0;
     if (R < 0 || row_bytes <= 0 || row_bytes % 16 != 0) return fail(DSV4_ERR_ARG, "gather_rows: row_bytes must be a positive multiple of 16");
     if (src == nullptr || dst == nullptr || src_row == nullptr) return fail(DSV4_ERR_ARG, "gather_rows: null pointer");
     if ((reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15))
         return fail(DSV4_ERR_ARG, "gather_rows: src and dst must be 16-byte aligned");
     gather_rows_kernel<<<R, 128, 0, st>>>(static_cast<const uint4*>(src), src_row, static_cast<uint4*>(dst), R,
-                                          row_bytes / 16, src_scale, dst_scale, scales_per_row);
+                                          row_bytes / 16, src_scale, dst_scale, scales_per_row, valid_rows);
     return check_launch("gather_rows");
 }
 

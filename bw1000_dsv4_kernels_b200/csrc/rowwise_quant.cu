@@ -401,11 +401,12 @@ __global__ void __launch_bounds__(kSumLanes) rmsnorm_generic_kernel(__nv_bfloat1
 template <int T, int MINB>
 __global__ void __launch_bounds__(T, MINB) silu_mul_quant_vec_kernel(
     const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
-    const int* __restrict__ mask, int8_t* __restrict__ q, float* __restrict__ s, int M, int N,
-    int64_t ldg, int64_t ldu) {
+    const int* __restrict__ mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
+    float* __restrict__ s, int M, int N, int64_t ldg, int64_t ldu) {
     extern __shared__ float4 h_row4[];  // N floats, 16-byte aligned
     __shared__ float red[32];
     const int V = N >> 3, tid = threadIdx.x;
+    if (valid_rows != nullptr) M = min(M, __ldg(valid_rows));
     for (int row = blockIdx.x; row < M; row += gridDim.x) {
         if (mask != nullptr && mask[row] == 0) continue;  // uniform over the block
         const uint4* gr = reinterpret_cast<const uint4*>(g + (int64_t)row * ldg);
@@ -458,9 +459,10 @@ __global__ void __launch_bounds__(T, MINB) silu_mul_quant_vec_kernel(
 
 __global__ void __launch_bounds__(256) silu_mul_quant_generic_kernel(
     const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
-    const int* __restrict__ mask, int8_t* __restrict__ q, float* __restrict__ s, int M, int N,
-    int64_t ldg, int64_t ldu) {
+    const int* __restrict__ mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
+    float* __restrict__ s, int M, int N, int64_t ldg, int64_t ldu) {
     __shared__ float red[32];
+    if (valid_rows != nullptr) M = min(M, __ldg(valid_rows));
     for (int row = blockIdx.x; row < M; row += gridDim.x) {
         if (mask != nullptr && mask[row] == 0) continue;
         const __nv_bfloat16* gr = g + (int64_t)row * ldg;
@@ -630,8 +632,8 @@ int rmsnorm(void* x, int M, int K, float eps, cudaStream_t st) {
     return check_launch("rmsnorm");
 }
 
-int silu_mul_quant(const void* g, const void* u, const int* mask, void* q, void* s, int M, int N,
-                   int64_t ldg, int64_t ldu, cudaStream_t st) {
+int silu_mul_quant(const void* g, const void* u, const int* mask, const int* valid_rows, void* q, void* s,
+                   int M, int N, int64_t ldg, int64_t ldu, cudaStream_t st) {
     if (M == 0 || N == 0) return 0;
     auto gp = static_cast<const __nv_bfloat16*>(g);
     auto up = static_cast<const __nv_bfloat16*>(u);
@@ -653,13 +655,13 @@ int silu_mul_quant(const void* g, const void* u, const int* mask, void* q, void*
             if (dev >= 0 && dev < 64) opted_in[dev] = true;
         }
         if (V <= 256)
-            silu_mul_quant_vec_kernel<128, 8><<<grid_rows(M), 128, row_smem, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
+            silu_mul_quant_vec_kernel<128, 8><<<grid_rows(M), 128, row_smem, st>>>(gp, up, mask, valid_rows, qp, sp, M, N, ldg, ldu);
         else if (V <= 1024)
-            silu_mul_quant_vec_kernel<256, 4><<<grid_rows(M), 256, row_smem, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
+            silu_mul_quant_vec_kernel<256, 4><<<grid_rows(M), 256, row_smem, st>>>(gp, up, mask, valid_rows, qp, sp, M, N, ldg, ldu);
         else
-            silu_mul_quant_vec_kernel<384, 3><<<grid_rows(M), 384, row_smem, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
+            silu_mul_quant_vec_kernel<384, 3><<<grid_rows(M), 384, row_smem, st>>>(gp, up, mask, valid_rows, qp, sp, M, N, ldg, ldu);
     } else {
-        silu_mul_quant_generic_kernel<<<grid_rows(M), 256, 0, st>>>(gp, up, mask, qp, sp, M, N, ldg, ldu);
+        silu_mul_quant_generic_kernel<<<grid_rows(M), 256, 0, st>>>(gp, up, mask, valid_rows, qp, sp, M, N, ldg, ldu);
     }
     return check_launch("silu_mul_quant");
 }

@@ -139,6 +139,18 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
         : "memory");
 }
 
+// 16 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
 // ---- CTA pairs (cta_group::2) --------------------------------------------------------
 // Two CTAs of a cluster work on one 256-row tile: each loads its own 128 rows of A and its
 // own half of B's rows into its own shared memory, the even CTA issues the MMAs for both,
@@ -201,6 +213,26 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask) 
         "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
         ::"r"(bar), "h"(cta_mask)
         : "memory");
+}
+
+// 32-bit load from a shared::cluster address (own or peer CTA's shared memory)
+__device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr) {
+    uint32_t v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 ld_shared_cluster_v4(uint32_t cluster_addr) {
+    uint4 v;
+    asm volatile("ld.shared::cluster.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(cluster_addr)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
 }
 
 // ---- descriptors ------------------------------------------------------------------

@@ -139,7 +139,23 @@ std::vector<Tensor> silu_mul_quant_stream(Tensor gate, Tensor up, int64_t stream
     c10::cuda::CUDAGuard guard(gate.device());
     auto q = torch::empty({g.M, g.N}, gate.options().dtype(torch::kInt8));
     auto s = torch::empty({g.M}, gate.options().dtype(torch::kFloat32));
-    check_status(launch_silu_mul_quant_strided(gate.data_ptr(), g.ldg, up.data_ptr(), g.ldu, nullptr, q.data_ptr(),
+    check_status(launch_silu_mul_quant_strided(gate.data_ptr(), g.ldg, up.data_ptr(), g.ldu, nullptr, nullptr,
+                                               q.data_ptr(), s.data_ptr(), g.M, g.N, as_stream(stream_ptr)));
+    return {q, s.unsqueeze(-1)};
+}
+
+// Same, but only the first min(M, valid_rows[0]) rows are processed; valid_rows is a one-element
+// int32 CUDA tensor (the routed-row count of an expert-parallel rank lives on the device).
+// Rows beyond it are returned as zero.
+std::vector<Tensor> silu_mul_quant_rows_stream(Tensor gate, Tensor up, Tensor valid_rows, int64_t stream_ptr) {
+    const GateUp g = check_gate_up(gate, up);
+    check_cuda(valid_rows, "valid_rows", torch::kInt32);
+    TORCH_CHECK(valid_rows.numel() >= 1, "valid_rows must hold one int32");
+    c10::cuda::CUDAGuard guard(gate.device());
+    auto q = torch::zeros({g.M, g.N}, gate.options().dtype(torch::kInt8));
+    auto s = torch::zeros({g.M}, gate.options().dtype(torch::kFloat32));
+    check_status(launch_silu_mul_quant_strided(gate.data_ptr(), g.ldg, up.data_ptr(), g.ldu, nullptr,
+                                               static_cast<const int*>(valid_rows.data_ptr()), q.data_ptr(),
                                                s.data_ptr(), g.M, g.N, as_stream(stream_ptr)));
     return {q, s.unsqueeze(-1)};
 }
@@ -154,8 +170,8 @@ std::vector<Tensor> silu_mul_masked_quant_stream(Tensor gate, Tensor up, Tensor 
     auto q = torch::zeros({g.M, g.N}, gate.options().dtype(torch::kInt8));
     auto s = torch::zeros({g.M}, gate.options().dtype(torch::kFloat32));
     check_status(launch_silu_mul_quant_strided(gate.data_ptr(), g.ldg, up.data_ptr(), g.ldu,
-                                               static_cast<const int*>(mask.data_ptr()), q.data_ptr(), s.data_ptr(),
-                                               g.M, g.N, as_stream(stream_ptr)));
+                                               static_cast<const int*>(mask.data_ptr()), nullptr, q.data_ptr(),
+                                               s.data_ptr(), g.M, g.N, as_stream(stream_ptr)));
     return {q, s.unsqueeze(-1)};
 }
 
@@ -261,7 +277,7 @@ Tensor grouped_gemm_stream(Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor expe
     return C;
 }
 
-std::vector<Tensor> moe_segments_stream(Tensor topk_ids, int64_t num_experts, int64_t stream_ptr) {
+std::vector<Tensor> moe_segments_stream(Tensor topk_ids, int64_t num_experts, int64_t expert_lo, int64_t stream_ptr) {
     check_cuda(topk_ids, "topk_ids", torch::kInt32);
     TORCH_CHECK(topk_ids.dim() == 2 && topk_ids.is_contiguous(), "topk_ids must be a contiguous [T,topk] tensor");
     c10::cuda::CUDAGuard guard(topk_ids.device());
@@ -275,14 +291,16 @@ std::vector<Tensor> moe_segments_stream(Tensor topk_ids, int64_t num_experts, in
         return {offsets, src_row, dst_slot};
     }
     check_status(launch_moe_segments(static_cast<const int*>(topk_ids.data_ptr()), T, topk,
-                                     to_int(num_experts, "num_experts"), static_cast<int*>(offsets.data_ptr()),
+                                     to_int(num_experts, "num_experts"), to_int(expert_lo, "expert_lo"),
+                                     static_cast<int*>(offsets.data_ptr()),
                                      static_cast<int*>(src_row.data_ptr()), static_cast<int*>(dst_slot.data_ptr()),
                                      as_stream(stream_ptr)));
     return {offsets, src_row, dst_slot};
 }
 
 // rows of `src` ([T, row]) gathered by src_row; `scales` ([T, spr] or [T,1]) optional
-std::vector<Tensor> gather_rows_stream(Tensor src, Tensor src_row, c10::optional<Tensor> scales, int64_t stream_ptr) {
+std::vector<Tensor> gather_rows_stream(Tensor src, Tensor src_row, c10::optional<Tensor> scales,
+                                       c10::optional<Tensor> valid_rows, int64_t stream_ptr) {
     TORCH_CHECK(src.is_cuda() && src.dim() == 2 && src.is_contiguous(), "src must be a contiguous 2-D CUDA tensor");
     check_cuda(src_row, "src_row", torch::kInt32);
     TORCH_CHECK(src_row.is_contiguous(), "src_row must be contiguous");
@@ -304,10 +322,46 @@ std::vector<Tensor> gather_rows_stream(Tensor src, Tensor src_row, c10::optional
         sp = static_cast<const float*>(sc.data_ptr());
         dp = static_cast<float*>(dscale.data_ptr());
     }
+    const int* vr = nullptr;
+    if (valid_rows.has_value()) {
+        check_cuda(*valid_rows, "valid_rows", torch::kInt32);
+        vr = static_cast<const int*>(valid_rows->data_ptr());
+    }
     check_status(launch_gather_rows(src.data_ptr(), static_cast<const int*>(src_row.data_ptr()), dst.data_ptr(), R,
-                                    to_int(row_bytes, "row bytes"), sp, dp, spr, as_stream(stream_ptr)));
+                                    to_int(row_bytes, "row bytes"), sp, dp, spr, vr, as_stream(stream_ptr)));
     if (scales.has_value()) return {dst, dscale};
     return {dst};
+}
+
+// out[t] = sum_j w[t,j] * z[dst_slot[t,j]]  (bf16, or fp32 partial sums when out_f32)
+Tensor moe_combine_stream(Tensor z, Tensor dst_slot, Tensor topk_w, bool out_f32, int64_t stream_ptr) {
+    check_cuda(z, "z", torch::kBFloat16);
+    check_cuda(dst_slot, "dst_slot", torch::kInt32);
+    check_cuda(topk_w, "topk_w", torch::kFloat32);
+    TORCH_CHECK(z.dim() == 2 && z.is_contiguous() && topk_w.dim() == 2 && topk_w.is_contiguous() &&
+                dst_slot.is_contiguous() && dst_slot.numel() == topk_w.numel(),
+                "z must be [R,H], topk_w [T,topk], dst_slot T*topk entries, all contiguous");
+    c10::cuda::CUDAGuard guard(z.device());
+    const int T = to_int(topk_w.size(0), "T"), topk = to_int(topk_w.size(1), "topk"), H = to_int(z.size(1), "H");
+    auto out = torch::empty({T, H}, z.options().dtype(out_f32 ? torch::kFloat32 : torch::kBFloat16));
+    check_status(launch_moe_combine(z.data_ptr(), static_cast<const int*>(dst_slot.data_ptr()),
+                                    static_cast<const float*>(topk_w.data_ptr()), out.data_ptr(), T, topk, H,
+                                    out_f32 ? 1 : 0, as_stream(stream_ptr)));
+    return out;
+}
+
+// w8a8 GEMM written into columns [col0, col0 + N) of an existing bf16 [M, ldc] buffer
+void w8a8_gemm_into_stream(Tensor A, Tensor B, Tensor sa, Tensor sb, Tensor out, int64_t col0, int64_t stream_ptr) {
+    const GemmShape g = check_gemm_operands(A, B);
+    auto sa_c = flat_scale(sa, g.M, "sa");
+    auto sb_c = flat_scale(sb, g.N, "sb");
+    check_cuda(out, "out", torch::kBFloat16);
+    TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1 && out.size(0) == g.M && col0 >= 0 && col0 + g.N <= out.size(1),
+                "out must be a [M, >= col0 + N] bf16 tensor with unit inner stride");
+    c10::cuda::CUDAGuard guard(A.device());
+    auto* base = static_cast<at::BFloat16*>(out.data_ptr()) + col0;
+    check_status(launch_w8a8_gemm_ld(A.data_ptr(), B.data_ptr(), sa_c.data_ptr(), sb_c.data_ptr(), base, out.stride(0),
+                                     g.M, g.N, g.K, as_stream(stream_ptr)));
 }
 
 int64_t device_status() {
@@ -360,12 +414,26 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         return grouped_gemm_stream(A, W, sa, sw, off, current_stream_ptr());
     });
     m.def("grouped_gemm_stream", &grouped_gemm_stream);
-    m.def("moe_segments", [](Tensor ids, int64_t E) { return moe_segments_stream(ids, E, current_stream_ptr()); });
+    m.def("moe_segments", [](Tensor ids, int64_t E, int64_t lo) {
+        return moe_segments_stream(ids, E, lo, current_stream_ptr());
+    }, py::arg("topk_ids"), py::arg("num_experts"), py::arg("expert_lo") = 0);
     m.def("moe_segments_stream", &moe_segments_stream);
-    m.def("gather_rows", [](Tensor src, Tensor src_row, c10::optional<Tensor> scales) {
-        return gather_rows_stream(src, src_row, scales, current_stream_ptr());
-    }, py::arg("src"), py::arg("src_row"), py::arg("scales") = py::none());
+    m.def("gather_rows", [](Tensor src, Tensor src_row, c10::optional<Tensor> scales, c10::optional<Tensor> valid) {
+        return gather_rows_stream(src, src_row, scales, valid, current_stream_ptr());
+    }, py::arg("src"), py::arg("src_row"), py::arg("scales") = py::none(), py::arg("valid_rows") = py::none());
     m.def("gather_rows_stream", &gather_rows_stream);
+    m.def("silu_mul_quant_rows", [](Tensor g, Tensor u, Tensor valid) {
+        return silu_mul_quant_rows_stream(g, u, valid, current_stream_ptr());
+    });
+    m.def("silu_mul_quant_rows_stream", &silu_mul_quant_rows_stream);
+    m.def("moe_combine", [](Tensor z, Tensor slot, Tensor w, bool f32) {
+        return moe_combine_stream(z, slot, w, f32, current_stream_ptr());
+    }, py::arg("z"), py::arg("dst_slot"), py::arg("topk_w"), py::arg("out_f32") = false);
+    m.def("moe_combine_stream", &moe_combine_stream);
+    m.def("w8a8_gemm_into", [](Tensor A, Tensor B, Tensor sa, Tensor sb, Tensor out, int64_t col0) {
+        w8a8_gemm_into_stream(A, B, sa, sb, out, col0, current_stream_ptr());
+    });
+    m.def("w8a8_gemm_into_stream", &w8a8_gemm_into_stream);
     m.def("device_status", &device_status);
     m.def("abi_version", [] { return dsv4_abi_version(); });
 }

@@ -1,0 +1,67 @@
+"""Column-sharded tensor-parallel W8A8 linear layer.
+
+The [N, K] int8 weight is split on N over the G ranks of one node; the activation X [M, K] is
+replicated and every rank quantises it itself (per_token_quant_int8), computes its own slab
+C[:, r*N/G:(r+1)*N/G] with the int8 GEMM, and the slabs are exchanged so that every rank ends
+with the full bf16 [M, N].
+
+The reference has no collective code at all (its server ran `--tp 8` outside the repository,
+README.md:104); the exchange here is NCCL over NVLink:
+
+  * each rank's GEMM writes its slab into a slab-major buffer out_slabs[r] ([G, M, N/G], the
+    layout ncclAllGather produces), `all_gather_into_tensor` fills the other slabs in place;
+  * `row_major()` gives the [M, N] view consumers expect (one strided copy), or the slab-major
+    buffer can be consumed directly by a following row-sharded layer.
+"""
+import torch
+
+
+def _ext():
+    import bw1000_dsv4_kernels_b200 as pkg
+    return pkg.dsv4_native_ext
+
+
+def column_range(rank: int, world: int, n: int):
+    assert n % world == 0, "N must divide evenly over the ranks"
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+class ColumnParallelW8A8Linear:
+    def __init__(self, w_local, w_scale_local, rank: int = 0, world: int = 1, process_group=None):
+        """w_local int8 [N/G, K], w_scale_local fp32 [N/G] (this rank's rows of the weight)."""
+        self.w, self.w_scale = w_local, w_scale_local
+        self.rank, self.world, self.pg = rank, world, process_group
+        self.n_local = w_local.shape[0]
+        self._buf = None
+
+    def _slabs(self, m, device):
+        shape = (self.world, m, self.n_local)
+        if self._buf is None or self._buf.shape != shape or self._buf.device != device:
+            self._buf = torch.empty(shape, dtype=torch.bfloat16, device=device)
+        return self._buf
+
+    def local_gemm(self, x, out=None):
+        """quantise + GEMM for this rank's columns -> bf16 [M, N/G] (written into `out` if given)."""
+        ext = _ext()
+        q, s = ext.per_token_quant_int8(x)
+        if out is None:
+            return ext.w8a8_scaled_gemm(q, self.w, s, self.w_scale)
+        ext.w8a8_gemm_into(q, self.w, s, self.w_scale, out, 0)
+        return out
+
+    def forward_slabs(self, x):
+        """-> bf16 [G, M, N/G]: slab r holds columns [r*N/G, (r+1)*N/G) of the result."""
+        slabs = self._slabs(x.shape[0], x.device)
+        self.local_gemm(x, out=slabs[self.rank])
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_gather_into_tensor(slabs.view(-1), slabs[self.rank].reshape(-1), group=self.pg)
+        return slabs
+
+    def forward(self, x):
+        """-> bf16 [M, N] row-major."""
+        slabs = self.forward_slabs(x)
+        if self.world == 1:
+            return slabs[0]
+        return slabs.permute(1, 0, 2).reshape(x.shape[0], self.world * self.n_local)

@@ -84,10 +84,12 @@ DSV4_API int launch_silu_mul_masked_quant(const void* g, const void* u, const in
                                  int M, int N, dsv4_stream_t stream);
 
 /* Same with row strides (elements) so that g and u can be the halves of one packed
- * [M, 2N] gate_up tensor; mask may be null. */
+ * [M, 2N] gate_up tensor.  mask may be null.  valid_rows may be null; otherwise it points to
+ * one int32 ON THE DEVICE and only rows below min(M, *valid_rows) are processed (the row count
+ * of an expert-parallel rank is only known on the device). */
 DSV4_API int launch_silu_mul_quant_strided(const void* g, int64_t ldg, const void* u, int64_t ldu,
-                                  const int* mask, void* q, void* s, int M, int N,
-                                  dsv4_stream_t stream);
+                                  const int* mask, const int* valid_rows, void* q, void* s, int M,
+                                  int N, dsv4_stream_t stream);
 
 /* ---- unfused neighbours --------------------------------------------------------- */
 
@@ -110,6 +112,11 @@ DSV4_API int launch_w8a8_gemm(const void* A, const void* B, const void* sa, cons
                      int N, int K, dsv4_stream_t stream);
 DSV4_API int launch_w8a8_gemm_v5(const void* A, const void* B, const void* sa, const void* sb, void* C,
                         int M, int N, int K, dsv4_stream_t stream);
+
+/* Same with a row stride for C in elements (ldc >= N): the result can be written straight
+ * into a column slab of a wider [M, ldc] buffer, as a column-sharded linear layer needs. */
+DSV4_API int launch_w8a8_gemm_ld(const void* A, const void* B, const void* sa, const void* sb, void* C,
+                        int64_t ldc, int M, int N, int K, dsv4_stream_t stream);
 
 /* Raw accumulators: C int32 [M,N] = sum_k A[m,k]*B[n,k].  The product torch._int_mm
  * supplies in w8a8_gemm_intmm_fused.hip:38-39. */
@@ -137,18 +144,29 @@ DSV4_API int launch_grouped_gemm(const void* A, const void* W, const void* sa, c
                         int sa_groups, dsv4_stream_t stream);
 
 /* Segment offsets and the token permutation from top-k routing ids.
- * topk_ids int32 [T, topk] with values in [0,E) -> expert_offsets int32 [E+1];
- * src_row int32 [T*topk]: routed row r (in expert-sorted order) came from token src_row[r];
- * dst_slot int32 [T*topk]: pair (t, j) landed at routed row dst_slot[t*topk + j].
+ * topk_ids int32 [T, topk] -> expert_offsets int32 [E+1] for the E experts
+ * [expert_lo, expert_lo + E) (expert_lo = 0 and E = all experts on one GPU; a slice under
+ * expert parallelism);
+ * src_row int32 [T*topk]: routed row r (in expert-sorted order) came from token src_row[r],
+ *   valid for r < expert_offsets[E];
+ * dst_slot int32 [T*topk]: pair (t, j) landed at routed row dst_slot[t*topk + j], or -1 when
+ *   its expert is outside the slice.
  * Within an expert, rows keep increasing (t, j) order.  Uses no scratch memory. */
-DSV4_API int launch_moe_segments(const int* topk_ids, int T, int topk, int E, int* expert_offsets,
-                        int* src_row, int* dst_slot, dsv4_stream_t stream);
+DSV4_API int launch_moe_segments(const int* topk_ids, int T, int topk, int E, int expert_lo,
+                        int* expert_offsets, int* src_row, int* dst_slot, dsv4_stream_t stream);
 
-/* dst[r, :] = src[src_row[r], :] for r < R, rows of row_bytes bytes (multiple of 16);
- * optionally the same gather for fp32 scales with scales_per_row entries per row. */
+/* dst[r, :] = src[src_row[r], :] for r < R (and r < *valid_rows when valid_rows, a device
+ * pointer, is not null); rows of row_bytes bytes (multiple of 16); optionally the same gather
+ * for fp32 scales with scales_per_row entries per row. */
 DSV4_API int launch_gather_rows(const void* src, const int* src_row, void* dst, int R, int row_bytes,
                        const float* src_scale, float* dst_scale, int scales_per_row,
-                       dsv4_stream_t stream);
+                       const int* valid_rows, dsv4_stream_t stream);
+
+/* out[t, :] = sum_j topk_w[t,j] * z[dst_slot[t,j], :] over the token's top-k slots in order
+ * (fp32 fma accumulation; slots equal to -1 are skipped).  z bf16 [R,H]; out bf16 [T,H], or
+ * fp32 [T,H] when out_f32 != 0 (the partial sum an expert-parallel rank contributes). */
+DSV4_API int launch_moe_combine(const void* z, const int* dst_slot, const float* topk_w, void* out, int T,
+                       int topk, int H, int out_f32, dsv4_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -148,15 +148,29 @@ def grouped_gemm(A, W, sa, sw, expert_offsets):
     return out
 
 
-def moe_segments(topk_ids: torch.Tensor, num_experts: int):
+def moe_segments(topk_ids: torch.Tensor, num_experts: int, expert_lo: int = 0):
+    """-> (offsets [E+1], src_row [T*topk] (valid below offsets[-1]), dst_slot [T*topk] with -1 for
+    pairs routed outside [expert_lo, expert_lo + num_experts))."""
     ids = topk_ids.to(torch.int32).contiguous()
     t, topk = ids.shape
     off = torch.empty(num_experts + 1, dtype=torch.int32)
-    src = torch.empty(t * topk, dtype=torch.int32)
+    src = torch.full((t * topk,), -1, dtype=torch.int32)
     dst = torch.empty(t * topk, dtype=torch.int32)
-    lib().oracle_moe_segments(_p(ids), ctypes.c_int(t), ctypes.c_int(topk), ctypes.c_int(num_experts), _p(off),
-                              _p(src), _p(dst))
+    lib().oracle_moe_segments(_p(ids), ctypes.c_int(t), ctypes.c_int(topk), ctypes.c_int(num_experts),
+                              ctypes.c_int(expert_lo), _p(off), _p(src), _p(dst))
     return off, src, dst
+
+
+def moe_combine(z: torch.Tensor, dst_slot: torch.Tensor, topk_w: torch.Tensor, out_f32: bool = False):
+    z = z.contiguous()
+    t, topk = topk_w.shape
+    h = z.shape[1]
+    out = torch.empty((t, h), dtype=torch.float32 if out_f32 else torch.bfloat16)
+    null = ctypes.c_void_p(0)
+    lib().oracle_moe_combine(_p(z), _p(dst_slot.to(torch.int32).contiguous()), _p(topk_w.contiguous().float()),
+                             null if out_f32 else _p(out), _p(out) if out_f32 else null, ctypes.c_int(t),
+                             ctypes.c_int(topk), ctypes.c_int(h))
+    return out
 
 
 def exp_fixed(x: float) -> float:

@@ -354,19 +354,47 @@ void oracle_grouped_gemm(const int8_t* A, const int8_t* W, const float* sa, cons
     }
 }
 
-/* Stable counting sort of (token, slot) pairs by expert id. */
-void oracle_moe_segments(const int32_t* ids, int T, int topk, int E, int32_t* off, int32_t* src_row,
+/* Stable counting sort of (token, slot) pairs by expert id, restricted to the experts
+ * [lo, lo + E): pairs routed elsewhere get dst_slot -1 and no row. */
+void oracle_moe_segments(const int32_t* ids, int T, int topk, int E, int lo, int32_t* off, int32_t* src_row,
                          int32_t* dst_slot) {
     const int R = T * topk;
     for (int e = 0; e <= E; ++e) off[e] = 0;
-    for (int i = 0; i < R; ++i) off[ids[i] + 1]++;
+    for (int i = 0; i < R; ++i) {
+        const int e = ids[i] - lo;
+        if (e >= 0 && e < E) off[e + 1]++;
+    }
     for (int e = 0; e < E; ++e) off[e + 1] += off[e];
     int32_t* cur = (int32_t*)malloc(sizeof(int32_t) * (size_t)E);
     for (int e = 0; e < E; ++e) cur[e] = off[e];
     for (int i = 0; i < R; ++i) {
-        const int r = cur[ids[i]]++;
-        src_row[r] = i / topk;
-        dst_slot[i] = r;
+        const int e = ids[i] - lo;
+        if (e >= 0 && e < E) {
+            const int r = cur[e]++;
+            src_row[r] = i / topk;
+            dst_slot[i] = r;
+        } else {
+            dst_slot[i] = -1;
+        }
     }
     free(cur);
+}
+
+/* Weighted sum of a token's expert outputs (the engine's moe_sum step,
+ * DSV4_OPERATOR_ANALYSIS.md:48): acc = fma(w[t,j], z[slot], acc) over j in order, fp32;
+ * out_bf16 (RNE) or out_f32, whichever is not NULL. */
+void oracle_moe_combine(const uint16_t* z, const int32_t* dst_slot, const float* w, uint16_t* out_bf16,
+                        float* out_f32, int T, int topk, int H) {
+#pragma omp parallel for schedule(static)
+    for (int t = 0; t < T; ++t)
+        for (int h = 0; h < H; ++h) {
+            float acc = 0.0f;
+            for (int j = 0; j < topk; ++j) {
+                const int slot = dst_slot[(int64_t)t * topk + j];
+                if (slot < 0) continue;
+                acc = fmaf(w[(int64_t)t * topk + j], bf16_to_f32(z[(int64_t)slot * H + h]), acc);
+            }
+            if (out_f32) out_f32[(int64_t)t * H + h] = acc;
+            if (out_bf16) out_bf16[(int64_t)t * H + h] = f32_to_bf16(acc);
+        }
 }

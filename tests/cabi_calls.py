@@ -82,12 +82,12 @@ def silu_mul(g, u):
     return out
 
 
-def silu_mul_quant(g, u, mask=None):
+def silu_mul_quant(g, u, mask=None, valid_rows=None):
     m, n = g.shape
     q = torch.zeros((m, n), dtype=torch.int8, device=g.device)
     s = torch.zeros(m, dtype=torch.float32, device=g.device)
     _check(lib().launch_silu_mul_quant_strided(_p(g), ctypes.c_int64(g.stride(0)), _p(u), ctypes.c_int64(u.stride(0)),
-                                               _p(mask), _p(q), _p(s), m, n, _stream()))
+                                               _p(mask), _p(valid_rows), _p(q), _p(s), m, n, _stream()))
     return q, s.unsqueeze(-1)
 
 
@@ -123,16 +123,33 @@ def grouped_gemm(A, W, sa, sw, off):
     return C
 
 
-def moe_segments(ids, num_experts):
+def moe_segments(ids, num_experts, expert_lo=0):
     t, topk = ids.shape
     off = torch.empty(num_experts + 1, dtype=torch.int32, device=ids.device)
-    src = torch.empty(t * topk, dtype=torch.int32, device=ids.device)
+    src = torch.full((t * topk,), -1, dtype=torch.int32, device=ids.device)
     dst = torch.empty(t * topk, dtype=torch.int32, device=ids.device)
-    _check(lib().launch_moe_segments(_p(ids), t, topk, num_experts, _p(off), _p(src), _p(dst), _stream()))
+    _check(lib().launch_moe_segments(_p(ids), t, topk, num_experts, expert_lo, _p(off), _p(src), _p(dst), _stream()))
     return off, src, dst
 
 
-def gather_rows(src, src_row, scales=None):
+def moe_combine(z, dst_slot, topk_w, out_f32=False):
+    t, topk = topk_w.shape
+    out = torch.empty((t, z.shape[1]), dtype=torch.float32 if out_f32 else torch.bfloat16, device=z.device)
+    _check(lib().launch_moe_combine(_p(z), _p(dst_slot), _p(topk_w), _p(out), t, topk, z.shape[1], int(out_f32),
+                                    _stream()))
+    return out
+
+
+def w8a8_gemm_ld(A, B, sa, sb, out, col0):
+    m, k = A.shape
+    n = B.shape[0]
+    base = ctypes.c_void_p(out.data_ptr() + 2 * col0)
+    _check(lib().launch_w8a8_gemm_ld(_p(A), _p(B), _p(sa), _p(sb), base, ctypes.c_int64(out.stride(0)), m, n, k,
+                                     _stream()))
+    return out
+
+
+def gather_rows(src, src_row, scales=None, valid_rows=None):
     r = src_row.numel()
     dst = torch.empty((r, src.shape[1]), dtype=src.dtype, device=src.device)
     ds = None
@@ -141,7 +158,7 @@ def gather_rows(src, src_row, scales=None):
         spr = scales.shape[1]
         ds = torch.empty((r, spr), dtype=torch.float32, device=src.device)
     _check(lib().launch_gather_rows(_p(src), _p(src_row), _p(dst), r, src.shape[1] * src.element_size(), _p(scales),
-                                    _p(ds), spr, _stream()))
+                                    _p(ds), spr, _p(valid_rows), _stream()))
     return dst, ds
 
 

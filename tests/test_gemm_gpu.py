@@ -184,3 +184,43 @@ def test_grouped_gemm_matches_oracle(cabi, ext, seg_lens, n, k):
     _check_bf16(out, ref, "C-ABI")
     out2 = ext.grouped_gemm(A.cuda(), W.cuda(), sa.cuda().unsqueeze(-1), sw.cuda(), off.cuda())
     _check_bf16(out2, ref, "operator")
+
+
+@pytest.mark.parametrize("seg_lens,n,k", [
+    ([128, 128], 256, 256),
+    ([5, 0, 300, 128, 1, 0, 77], 520, 384),
+    ([0, 0, 9], 72, 128),
+    ([64, 200, 17, 129, 255, 3, 0, 90], 4096, 7168),
+])
+def test_group_scaled_grouped_gemm_matches_oracle(cabi, ext, seg_lens, n, k):
+    # one activation scale per (row, 128 columns of K): y = fma(float(acc_g), s[r,g], y), then * sw
+    A, W, _, sw, off = _grouped_case(seg_lens, n, k, seed=3 * len(seg_lens) + n)
+    r = A.shape[0]
+    sg = (wl.channel_scales((r, k // 128), seed=77) * 3.0).contiguous()
+    ref = oracle.grouped_gemm(A, W, sg, sw, off)
+    out = cabi.grouped_gemm(A.cuda(), W.cuda(), sg.cuda(), sw.cuda(), off.cuda())
+    assert cabi.device_status() == 0
+    _check_bf16(out, ref, "C-ABI")
+    out2 = ext.grouped_gemm(A.cuda(), W.cuda(), sg.cuda(), sw.cuda(), off.cuda())
+    _check_bf16(out2, ref, "operator")
+
+
+def test_gemm_writes_into_column_slab(cabi, ext):
+    # the column-sharded linear writes each rank's result into a slab of a wider buffer (ldc > N)
+    m, n, k, width = 300, 256, 512, 1024
+    A, B, sa, sb = _operands(m, n, k, seed=5)
+    ref = oracle.w8a8_gemm(A, B, sa, sb)
+    buf = torch.full((m, width), 7.0, dtype=torch.bfloat16, device="cuda")
+    cabi.w8a8_gemm_ld(A.cuda(), B.cuda(), sa.cuda(), sb.cuda(), buf, 512)
+    assert torch.equal(buf[:, 512:768].cpu().view(torch.int16), ref.view(torch.int16))
+    assert (buf[:, :512] == 7.0).all() and (buf[:, 768:] == 7.0).all()
+    buf2 = torch.zeros((m, width), dtype=torch.bfloat16, device="cuda")
+    ext.w8a8_gemm_into(A.cuda(), B.cuda(), sa.cuda(), sb.cuda(), buf2, 256)
+    assert torch.equal(buf2[:, 256:512].cpu().view(torch.int16), ref.view(torch.int16))
+    # large enough for the CTA-pair kernel
+    m, n, k = 2048, 2048, 256
+    A, B, sa, sb = _operands(m, n, k, seed=6)
+    buf3 = torch.zeros((m, 4096), dtype=torch.bfloat16, device="cuda")
+    cabi.w8a8_gemm_ld(A.cuda(), B.cuda(), sa.cuda(), sb.cuda(), buf3, 2048)
+    assert torch.equal(buf3[:, 2048:].cpu().view(torch.int16), oracle.w8a8_gemm(A, B, sa, sb).view(torch.int16))
+    assert buf3[:, :2048].abs().sum().item() == 0

@@ -35,3 +35,104 @@ def test_gather_rows(cabi, ext):
     xb = wl.randn_bf16((t, 512), seed=3)
     out = ext.gather_rows(xb.cuda(), idx.cuda())
     assert torch.equal(out[0].cpu().view(torch.int16), xb[idx.long()].view(torch.int16))
+
+
+@pytest.mark.parametrize("t,e,topk,lo,n_local", [(300, 64, 6, 16, 16), (77, 16, 2, 8, 8), (64, 8, 2, 0, 4)])
+def test_moe_segments_expert_slice(cabi, ext, t, e, topk, lo, n_local):
+    ids, _ = wl.moe_routing(t, e, topk, seed=t)
+    off_ref, src_ref, dst_ref = oracle.moe_segments(ids, n_local, lo)
+    off, src, dst = cabi.moe_segments(ids.cuda(), n_local, lo)
+    r = int(off_ref[-1])
+    assert torch.equal(off.cpu(), off_ref) and torch.equal(dst.cpu(), dst_ref)
+    assert torch.equal(src.cpu()[:r], src_ref[:r])
+    off2, src2, dst2 = ext.moe_segments(ids.cuda(), n_local, lo)
+    assert torch.equal(off2.cpu(), off_ref) and torch.equal(dst2.cpu(), dst_ref) and torch.equal(src2.cpu()[:r], src_ref[:r])
+    inside = (ids >= lo) & (ids < lo + n_local)
+    assert torch.equal(dst_ref.view(t, topk) >= 0, inside)
+
+
+def test_gather_rows_and_silu_respect_device_row_count(cabi, ext):
+    t, k = 40, 1024
+    q = wl.int8_weights((t, k), seed=1)
+    idx = torch.randint(0, t, (100,), dtype=torch.int32, generator=torch.Generator().manual_seed(0))
+    valid = torch.tensor([37], dtype=torch.int32).cuda()
+    dq, _ = cabi.gather_rows(q.cuda(), idx.cuda(), None, valid)
+    assert torch.equal(dq.cpu()[:37], q[idx[:37].long()])
+    gu = wl.randn_bf16((100, 512), seed=2)
+    qh_ref, sh_ref = oracle.silu_mul_quant(gu[:37, :256], gu[:37, 256:])
+    gud = gu.cuda()
+    qh, sh = ext.silu_mul_quant_rows(gud[:, :256], gud[:, 256:], valid)
+    assert torch.equal(qh.cpu()[:37], qh_ref) and torch.equal(sh.cpu()[:37], sh_ref)
+    assert qh[37:].abs().sum().item() == 0 and sh[37:].abs().sum().item() == 0
+
+
+@pytest.mark.parametrize("out_f32", [False, True])
+def test_moe_combine_matches_oracle(cabi, ext, out_f32):
+    t, topk, h, e = 50, 4, 512, 8
+    ids, w = wl.moe_routing(t, e, topk, seed=3)
+    _, _, dst = oracle.moe_segments(ids, 4, 2)          # half of the experts: some slots are -1
+    r = t * topk
+    z = wl.randn_bf16((r, h), seed=4)
+    ref = oracle.moe_combine(z, dst, w, out_f32)
+    out = cabi.moe_combine(z.cuda(), dst.cuda(), w.cuda(), out_f32)
+    out2 = ext.moe_combine(z.cuda(), dst.cuda(), w.cuda(), out_f32)
+    if out_f32:
+        assert torch.equal(out.cpu(), ref) and torch.equal(out2.cpu(), ref)
+    else:
+        assert torch.equal(out.cpu().view(torch.int16), ref.view(torch.int16))
+        assert torch.equal(out2.cpu().view(torch.int16), ref.view(torch.int16))
+
+
+def _oracle_moe(inp, e, lo, hi, group_scaled, out_f32):
+    """The MoE chain with every step taken from the oracle."""
+    inter = inp.w2.shape[2]
+    if group_scaled:
+        q, s = oracle.per_token_group_quant_int8(inp.x, 128)
+    else:
+        q, s = oracle.per_token_quant_int8(inp.x)
+    off, src, dst = oracle.moe_segments(inp.topk_ids, hi - lo, lo)
+    r = int(off[-1])
+    a_q, a_s = q[src[:r].long()], s[src[:r].long()]
+    y = oracle.grouped_gemm(a_q, inp.w13, a_s, inp.w13_scale, off)
+    h_q, h_s = oracle.silu_mul_quant(y[:, :inter], y[:, inter:])
+    z = oracle.grouped_gemm(h_q, inp.w2, h_s.view(-1), inp.w2_scale, off)
+    zz = torch.zeros((inp.topk_ids.numel(), z.shape[1]), dtype=torch.bfloat16)
+    zz[:r] = z
+    return oracle.moe_combine(zz, dst, inp.topk_w, out_f32), (off, a_q, a_s, y, h_q, h_s, z, r)
+
+
+@pytest.mark.parametrize("group_scaled", [True, False])
+def test_moe_chain_matches_oracle(group_scaled):
+    from bw1000_dsv4_kernels_b200 import moe
+    t, h, e, inter, topk = 96, 512, 8, 256, 2
+    inp = wl.moe_inputs(t, h, e, inter, topk, seed=9)
+    ref, (off, a_q, a_s, y, h_q, h_s, z, r) = _oracle_moe(inp, e, 0, e, group_scaled, False)
+    layer = moe.W8A8MoE(inp.w13.cuda(), inp.w13_scale.cuda(), inp.w2.cuda(), inp.w2_scale.cuda(), e,
+                        group_scaled=group_scaled)
+    out = layer.forward(inp.x.cuda(), inp.topk_ids.cuda(), inp.topk_w.cuda(), keep_trace=True)
+    tr = layer.last_trace
+    assert torch.equal(tr.offsets.cpu(), off)
+    assert torch.equal(tr.a_q.cpu()[:r], a_q) and torch.equal(tr.a_s.cpu()[:r], a_s)
+    assert torch.equal(tr.y.cpu()[:r].view(torch.int16), y.view(torch.int16)), "gate/up grouped GEMM"
+    assert torch.equal(tr.h_q.cpu()[:r], h_q) and torch.equal(tr.h_s.cpu()[:r], h_s), "silu_mul_quant"
+    assert torch.equal(tr.z.cpu()[:r].view(torch.int16), z.view(torch.int16)), "down grouped GEMM"
+    assert torch.equal(out.cpu().view(torch.int16), ref.view(torch.int16)), "combined output"
+
+
+def test_moe_expert_slice_partials_sum_to_full():
+    # two expert slices on one GPU: their fp32 partials add up to the single-rank result (to rounding)
+    from bw1000_dsv4_kernels_b200 import moe
+    t, h, e, inter, topk = 64, 512, 8, 256, 2
+    full = wl.moe_inputs(t, h, e, inter, topk, seed=11)
+    ref, _ = _oracle_moe(full, e, 0, e, True, False)
+    total = torch.zeros((t, h), dtype=torch.float32, device="cuda")
+    for lo, hi in ((0, 4), (4, 8)):
+        part_in = wl.moe_inputs(t, h, e, inter, topk, seed=11, expert_lo=lo, expert_hi=hi)
+        layer = moe.W8A8MoE(part_in.w13.cuda(), part_in.w13_scale.cuda(), part_in.w2.cuda(), part_in.w2_scale.cuda(),
+                            e, expert_lo=lo)
+        part = layer.local_partial(part_in.x.cuda(), part_in.topk_ids.cuda(), part_in.topk_w.cuda(), out_f32=True)
+        ref_part, _ = _oracle_moe(part_in, e, lo, hi, True, True)
+        assert torch.equal(part.cpu(), ref_part), "fp32 partial of an expert slice"
+        total += part
+    err = (total.cpu() - ref.float()).abs().max().item()
+    assert err <= 1e-2 * ref.float().abs().max().item()
