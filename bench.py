@@ -135,6 +135,28 @@ def time_launches(fn, iters: int, warmup: int = 3) -> float:
     return start.elapsed_time(end) / iters
 
 
+def time_launches_graph(fn, launches_per_graph: int = 20, replays: int = 10) -> float:
+    """Average milliseconds per call of fn(i) with the calls captured in a CUDA graph and the
+    graph replayed: the device time of short kernels without the host's per-call launch cost
+    (the serving engine this path plugs into replays it from CUDA graphs as well)."""
+    for i in range(3):
+        fn(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(launches_per_graph):
+            fn(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(replays):
+        graph.replay()
+    end.record()
+    end.synchronize()
+    return start.elapsed_time(end) / (replays * launches_per_graph)
+
+
 def rotation_count(bytes_per_set: int) -> int:
     """How many buffer sets to rotate through so that the footprint is well beyond L2."""
     return max(2, min(64, (3 * L2_BYTES + bytes_per_set - 1) // bytes_per_set))
@@ -256,14 +278,26 @@ def run_ours(args):
         q, sc = ext.add_rmsnorm_quant(s_.res, s_.x, gamma, 1e-6)
         return ext.w8a8_scaled_gemm(q, s_.w, sc, s_.w_scale)
 
+    # The K timed steps are replayed from CUDA graphs of up to 25 steps each (the serving engine
+    # this path plugs into replays it from CUDA graphs too); a remainder is launched directly.
+    per_graph = min(args.steps, 25)
+    n_replays, remainder = args.steps // per_graph, args.steps % per_graph
     sampler = ClockSampler(local_rank)
     with sampler:
         for i in range(max(args.warmup, 3)):
             step(i)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(per_graph):
+                step(i)
+        graph.replay()  # one untimed replay: first-use costs of the graph itself
         barrier()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        for i in range(args.steps):
+        for _ in range(n_replays):
+            graph.replay()
+        for i in range(remainder):
             step(i)
         end.record()
         end.synchronize()
@@ -275,12 +309,22 @@ def run_ours(args):
             ms_total = float(t.item())
         ms_step = ms_total / args.steps
 
+        if args.chain_only:
+            ops_step = 2.0 * M_ROWS * N_DIM * K_DIM
+            if rank == 0:
+                print(json.dumps({"metric": "W8A8 quant+GEMM TOPS", "value": ops_step * world / (ms_step * 1e-3) / 1e12,
+                                  "unit": "TOPS", "ms_per_step": ms_step, "steps": args.steps, "n_gpus": world,
+                                  "note": "--chain-only: the timed chain alone (for profiler launch lists)"}), flush=True)
+            if world > 1:
+                dist.destroy_process_group()
+            return
+
         # ---- per-kernel durations of the same launches (their own timed loops) -----------
         qs = [ext.add_rmsnorm_quant(s_.res, s_.x, gamma, 1e-6) for s_ in sets]
         iters = max(20, min(args.steps, 200))
-        ms_quant = time_launches(lambda i: ext.add_rmsnorm_quant(sets[i % nsets].res, sets[i % nsets].x, gamma, 1e-6), iters)
-        ms_gemm = time_launches(lambda i: ext.w8a8_scaled_gemm(qs[i % nsets][0], sets[i % nsets].w, qs[i % nsets][1],
-                                                              sets[i % nsets].w_scale), iters)
+        ms_quant = time_launches_graph(lambda i: ext.add_rmsnorm_quant(sets[i % nsets].res, sets[i % nsets].x, gamma, 1e-6))
+        ms_gemm = time_launches_graph(lambda i: ext.w8a8_scaled_gemm(qs[i % nsets][0], sets[i % nsets].w, qs[i % nsets][1],
+                                                                    sets[i % nsets].w_scale))
 
         # ---- end to end through the operator module with host buffers --------------------
         e2e_steps = max(3, min(args.steps, 30))
@@ -310,7 +354,7 @@ def run_ours(args):
         if not args.no_extras:
             try:
                 from bw1000_dsv4_kernels_b200 import bench_extras
-                extra = bench_extras.run(ext, dev, rank, world, peaks, time_launches, rotation_count)
+                extra = bench_extras.run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launches_graph)
             except Exception as exc:  # extras never take the headline down
                 extra = {"error": f"{type(exc).__name__}: {exc}"}
 
@@ -331,6 +375,7 @@ def run_ours(args):
             "l2": f"inputs and weights rotate through {nsets} buffer sets ({nsets * set_bytes / 1e6:.0f} MB) "
                   f"> 126 MB L2",
             "eps": 1e-6,
+            "launch": f"timed steps replayed from CUDA graphs of {per_graph} steps",
         },
         "roofline": {
             "kernel": "gemm_i8_kernel<256,4> (tcgen05 kind::i8)", "bound": "tensor", "achieved": gemm_tops,
@@ -398,6 +443,20 @@ def run_single_kernel(args):
         xs = [wl.activations_with_outliers(m, K, device=dev, seed=i) for i in range(nsets)]
         fn = lambda i: ext.per_token_quant_int8(xs[i % nsets])
         work = {"bytes": 3 * m * K + 4 * m}
+    elif args.kernel in ("grouped", "grouped_gs"):
+        # 16 experts x `m` rows each (default 128), gate/up shape: N=4096, K=7168
+        rows = 128 if m == M_ROWS else m
+        E, N2 = 16, 2 * wl.MOE_INTER
+        off = torch.arange(0, (E + 1) * rows, rows, dtype=torch.int32, device=dev)
+        A = wl.int8_weights((E * rows, K), device=dev, seed=1)
+        W = [wl.int8_weights((E, N2, K), device=dev, seed=10 + i) for i in range(2)]
+        sw = wl.channel_scales((E, N2), device=dev, seed=3)
+        if args.kernel == "grouped_gs":
+            sa = wl.channel_scales((E * rows, K // 128), device=dev, seed=2)
+        else:
+            sa = wl.channel_scales((E * rows,), device=dev, seed=2)
+        fn = lambda i: ext.grouped_gemm(A, W[i % 2], sa, sw, off)
+        work = {"ops": 2.0 * E * rows * N2 * K, "bytes": E * N2 * K + E * rows * (K + 2 * N2)}
     elif args.kernel == "ptgq":
         xs = [wl.randn_bf16((m, K), device=dev, seed=i) for i in range(nsets)]
         fn = lambda i: ext.per_token_group_quant_int8(xs[i % nsets], 128)
@@ -406,6 +465,8 @@ def run_single_kernel(args):
         raise SystemExit(f"unknown --kernel {args.kernel}")
     ms = time_launches(fn, args.steps, warmup=max(1, args.warmup))
     out = {"kernel": args.kernel, "m": m, "us": ms * 1e3, **work}
+    if args.graph:
+        out["us_graph"] = time_launches_graph(fn) * 1e3
     if "bytes" in work:
         out["GBps"] = work["bytes"] / (ms * 1e-3) / 1e9
     if "ops" in work:
@@ -416,14 +477,18 @@ def run_single_kernel(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default=None,
-                    help="run one kernel only: gemm, gemm_down, add_rmsnorm_quant, silu_mul_quant, ptq, ptgq")
+                    help="run one kernel only: gemm, gemm_down, grouped, grouped_gs, add_rmsnorm_quant, "
+                         "silu_mul_quant, ptq, ptgq")
     ap.add_argument("--m", type=int, default=M_ROWS, help="rows for --kernel")
+    ap.add_argument("--graph", action="store_true", help="with --kernel: also time CUDA-graph replays")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-configuration extras")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--chain-only", action="store_true",
+                    help="run the warm-up and the timed chain only (short launch list for a profiler)")
     args = ap.parse_args()
     if args.kernel is not None:
         run_single_kernel(args)

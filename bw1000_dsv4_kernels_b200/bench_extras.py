@@ -13,8 +13,12 @@ HBM = "hbm"
 TENSOR = "tensor"
 
 
-def _entry(us, peaks, bytes_=None, ops=None):
+def _entry(us, peaks, bytes_=None, ops=None, us_host_loop=None):
+    """`us` is the device time per launch (CUDA-graph replay where given); `us_host_loop` the
+    time per call when every call is launched from Python (adds the host's per-call cost)."""
     out = {"us": round(us, 3)}
+    if us_host_loop is not None:
+        out["us_host_loop"] = round(us_host_loop, 3)
     if bytes_ is not None:
         gbs = bytes_ / (us * 1e-6) / 1e9
         out.update({"bytes": int(bytes_), "GBps": round(gbs, 1), "hbm_frac": round(gbs / peaks["hbm_gbs"], 4)})
@@ -28,8 +32,15 @@ def _iters(us_guess):
     return int(max(10, min(200, 20000 / max(us_guess, 1.0))))
 
 
-def run(ext, dev, rank, world, peaks, time_launches, rotation_count):
-    res = {}
+def run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launches_graph):
+    res = {"timing": "us = per-launch device time from CUDA-graph replays of 20 launches over rotating buffers; "
+                     "us_host_loop = per-call time when launched one by one from Python"}
+
+    def both(fn, iters=100):
+        loop_us = 1e3 * time_launches(fn, iters)
+        graph_us = 1e3 * time_launches_graph(fn)
+        return graph_us, loop_us
+
     K, N1, I, H = wl.HIDDEN, wl.DENSE_N, wl.DENSE_INTER, wl.HIDDEN
 
     # ---- per_token_quant_int8 ------------------------------------------------------------
@@ -38,8 +49,8 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count):
         nb = m * K * 2
         n = rotation_count(nb * 3 // 2)
         xs = [wl.activations_with_outliers(m, K, device=dev, seed=i) for i in range(n)]
-        us = 1e3 * time_launches(lambda i: ext.per_token_quant_int8(xs[i % n]), 100)
-        sec[f"M={m}"] = _entry(us, peaks, bytes_=3 * m * K + 4 * m)
+        us, lp = both(lambda i: ext.per_token_quant_int8(xs[i % n]))
+        sec[f"M={m}"] = _entry(us, peaks, bytes_=3 * m * K + 4 * m, us_host_loop=lp)
         del xs
     res["per_token_quant_int8 K=7168"] = sec
 
@@ -48,13 +59,14 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count):
     for m in (4096,):
         n = rotation_count(m * K * 3)
         xs = [wl.randn_bf16((m, K), device=dev, seed=i) for i in range(n)]
-        us = 1e3 * time_launches(lambda i: ext.per_token_group_quant_int8(xs[i % n], 128), 100)
-        sec[f"M={m}"] = _entry(us, peaks, bytes_=3 * m * K + 4 * m * (K // 128))
+        us, lp = both(lambda i: ext.per_token_group_quant_int8(xs[i % n], 128))
+        sec[f"M={m}"] = _entry(us, peaks, bytes_=3 * m * K + 4 * m * (K // 128), us_host_loop=lp)
         del xs
     res["per_token_group_quant_int8 K=7168 gs=128"] = sec
 
     # ---- add_rmsnorm_quant -> w8a8_gemm --------------------------------------------------
-    w_sets = [wl.int8_weights((N1, K), device=dev, seed=50 + i) for i in range(5)]
+    NW = 8   # 8 x 29 MB of weights: far beyond the 126 MB L2
+    w_sets = [wl.int8_weights((N1, K), device=dev, seed=50 + i) for i in range(NW)]
     w_scale = wl.channel_scales((N1,), device=dev, seed=60)
     gamma = wl.gamma_bf16(K, device=dev, seed=2)
     quant_sec, gemm_sec = {}, {}
@@ -64,12 +76,13 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count):
         n = min(n, 48)
         xs = [wl.randn_bf16((m, K), device=dev, seed=i) for i in range(n)]
         rs = [wl.randn_bf16((m, K), device=dev, seed=100 + i) for i in range(n)]
-        us = 1e3 * time_launches(lambda i: ext.add_rmsnorm_quant(rs[i % n], xs[i % n], gamma, 1e-6), 100)
-        quant_sec[f"M={m}"] = _entry(us, peaks, bytes_=m * (7 * K + 4) + 2 * K)
+        us, lp = both(lambda i: ext.add_rmsnorm_quant(rs[i % n], xs[i % n], gamma, 1e-6))
+        quant_sec[f"M={m}"] = _entry(us, peaks, bytes_=m * (7 * K + 4) + 2 * K, us_host_loop=lp)
         qs = [ext.add_rmsnorm_quant(rs[i], xs[i], gamma, 1e-6) for i in range(min(n, 5))]
         nq = len(qs)
-        us = 1e3 * time_launches(lambda i: ext.w8a8_scaled_gemm(qs[i % nq][0], w_sets[i % 5], qs[i % nq][1], w_scale), 100)
-        gemm_sec[f"M={m}"] = _entry(us, peaks, bytes_=m * K + N1 * K + 2 * m * N1 + 4 * (m + N1), ops=2.0 * m * N1 * K)
+        us, lp = both(lambda i: ext.w8a8_scaled_gemm(qs[i % nq][0], w_sets[i % NW], qs[i % nq][1], w_scale))
+        gemm_sec[f"M={m}"] = _entry(us, peaks, bytes_=m * K + N1 * K + 2 * m * N1 + 4 * (m + N1), ops=2.0 * m * N1 * K,
+                                    us_host_loop=lp)
         del xs, rs, qs
     res["add_rmsnorm_quant K=7168"] = quant_sec
     res["w8a8_gemm N=4096 K=7168"] = gemm_sec
@@ -77,7 +90,7 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count):
     # library reference point only, not part of the product path
     try:
         a = wl.int8_weights((2048, K), device=dev, seed=7)
-        us = 1e3 * time_launches(lambda i: torch._int_mm(a, w_sets[i % 5].t()), 50)
+        us = 1e3 * time_launches(lambda i: torch._int_mm(a, w_sets[i % NW].t()), 50)
         res["library torch._int_mm M=2048 N=4096 K=7168 (int32 out, no epilogue)"] = _entry(us, peaks, ops=2.0 * 2048 * N1 * K)
         del a
     except Exception as exc:  # pragma: no cover
@@ -92,15 +105,120 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count):
         nb = m * 2 * I * 2
         n = max(2, min(rotation_count(nb), 24)) if m < 8192 else 2
         gus = [wl.randn_bf16((m, 2 * I), device=dev, seed=i) for i in range(n)]
-        us = 1e3 * time_launches(lambda i: ext.silu_mul_quant(gus[i % n][:, :I], gus[i % n][:, I:]), _iters(100 if m > 64 else 5))
-        silu_sec[f"M={m}"] = _entry(us, peaks, bytes_=m * (5 * I + 4))
+        us, lp = both(lambda i: ext.silu_mul_quant(gus[i % n][:, :I], gus[i % n][:, I:]), _iters(100 if m > 64 else 5))
+        silu_sec[f"M={m}"] = _entry(us, peaks, bytes_=m * (5 * I + 4), us_host_loop=lp)
         q, s = ext.silu_mul_quant(gus[0][:, :I], gus[0][:, I:])
         del gus
-        us = 1e3 * time_launches(lambda i: ext.w8a8_scaled_gemm(q, wd_sets[i % 2], s, wd_scale), _iters(150 if m > 64 else 30))
-        down_sec[f"M={m}"] = _entry(us, peaks, bytes_=m * I + H * I + 2 * m * H + 4 * (m + H), ops=2.0 * m * H * I)
+        us, lp = both(lambda i: ext.w8a8_scaled_gemm(q, wd_sets[i % 2], s, wd_scale), _iters(150 if m > 64 else 30))
+        down_sec[f"M={m}"] = _entry(us, peaks, bytes_=m * I + H * I + 2 * m * H + 4 * (m + H), ops=2.0 * m * H * I,
+                                    us_host_loop=lp)
         del q, s
     res["silu_mul_quant N=18432"] = silu_sec
     res["w8a8_gemm N=7168 K=18432"] = down_sec
     del wd_sets
     torch.cuda.empty_cache()
+
+    try:
+        res["moe_ffn T=4096 E=256 I=2048 top8"] = _moe_section(ext, dev, rank, world, peaks, time_launches)
+    except Exception as exc:  # pragma: no cover
+        res["moe_ffn"] = {"error": f"{type(exc).__name__}: {exc}"}
+    torch.cuda.empty_cache()
+    try:
+        res["tp_linear M=8192 K=7168 N=28672"] = _tp_section(ext, dev, rank, world, peaks, time_launches)
+    except Exception as exc:  # pragma: no cover
+        res["tp_linear"] = {"error": f"{type(exc).__name__}: {exc}"}
+    torch.cuda.empty_cache()
     return res
+
+
+def _max_over_ranks(ms, dev, world):
+    if world == 1:
+        return ms
+    import torch.distributed as dist
+    t = torch.tensor([ms], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _sync(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def _moe_section(ext, dev, rank, world, peaks, time_launches):
+    """MoE FFN, experts sharded over the ranks (expert parallel), tokens and routing replicated.
+    Weight-bandwidth-bound: ~128 routed rows per expert against 44 MB of int8 weights per expert."""
+    from . import moe
+    T, H, E, I, topk = wl.MOE_TOKENS, wl.HIDDEN, wl.MOE_EXPERTS, wl.MOE_INTER, wl.MOE_TOPK
+    lo, hi = moe.expert_range(rank, world, E)
+    inp = wl.moe_inputs(T, H, E, I, topk, device=dev, seed=0, expert_lo=lo, expert_hi=hi)
+    out = {}
+    for name, gs in (("group_scaled", True), ("per_token", False)):
+        layer = moe.W8A8MoE(inp.w13, inp.w13_scale, inp.w2, inp.w2_scale, E, expert_lo=lo, group_scaled=gs)
+        fwd = lambda i: layer.forward(inp.x, inp.topk_ids, inp.topk_w)
+        part = lambda i: layer.local_partial(inp.x, inp.topk_ids, inp.topk_w, out_f32=(world > 1))
+        _sync(world)
+        ms_local = _max_over_ranks(time_launches(part, 10, warmup=2), dev, world)
+        _sync(world)
+        ms_full = _max_over_ranks(time_launches(fwd, 10, warmup=2), dev, world)
+        rows_total = T * topk
+        ops = 2.0 * rows_total * (2 * I * H + H * I)
+        w_bytes = (hi - lo) * (2 * I * H + H * I)
+        out[name] = {
+            "ms_local_experts": round(ms_local, 4), "ms_with_allreduce": round(ms_full, 4),
+            "TOPS_whole_job": round(ops / (ms_full * 1e-3) / 1e12, 1),
+            "weight_GBps_per_rank": round(w_bytes / (ms_local * 1e-3) / 1e9, 1),
+            "weight_hbm_frac": round(w_bytes / (ms_local * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+            "experts_per_rank": hi - lo, "ranks": world,
+        }
+    # stage breakdown of the group-scaled chain on this rank
+    layer = moe.W8A8MoE(inp.w13, inp.w13_scale, inp.w2, inp.w2_scale, E, expert_lo=lo, group_scaled=True)
+    layer.local_partial(inp.x, inp.topk_ids, inp.topk_w, out_f32=False, keep_trace=True)
+    tr = layer.last_trace
+    q, sg = ext.per_token_group_quant_int8(inp.x, 128)
+    valid = tr.offsets[hi - lo:]
+    stages = {
+        "per_token_group_quant_int8": lambda i: ext.per_token_group_quant_int8(inp.x, 128),
+        "moe_segments": lambda i: ext.moe_segments(inp.topk_ids, hi - lo, lo),
+        "gather_rows": lambda i: ext.gather_rows(q, tr.src_row, sg, valid),
+        "grouped_gemm gate_up": lambda i: ext.grouped_gemm(tr.a_q, inp.w13, tr.a_s, inp.w13_scale, tr.offsets),
+        "silu_mul_quant": lambda i: ext.silu_mul_quant_rows(tr.y[:, :I], tr.y[:, I:], valid),
+        "grouped_gemm down": lambda i: ext.grouped_gemm(tr.h_q, inp.w2, tr.h_s, inp.w2_scale, tr.offsets),
+        "moe_combine": lambda i: ext.moe_combine(tr.z, tr.dst_slot, inp.topk_w, False),
+    }
+    out["stages_us_rank0"] = {k: round(1e3 * time_launches(f, 10, warmup=2), 1) for k, f in stages.items()}
+    return out
+
+
+def _tp_section(ext, dev, rank, world, peaks, time_launches):
+    """Column-sharded linear: quantise (replicated) + GEMM on N/G columns + NCCL all-gather."""
+    from . import tp_linear
+    M, K, N = wl.TP_M, wl.HIDDEN, wl.TP_N
+    inp = wl.tp_linear_inputs(rank, world, m=M, k=K, n=N, device=dev, seed=0)
+    layer = tp_linear.ColumnParallelW8A8Linear(inp.w, inp.w_scale, rank, world)
+    q, s = ext.per_token_quant_int8(inp.x)
+    _sync(world)
+    ms_gemm = _max_over_ranks(time_launches(lambda i: ext.w8a8_scaled_gemm(q, inp.w, s, inp.w_scale), 10, warmup=3), dev, world)
+    _sync(world)
+    ms_local = _max_over_ranks(time_launches(lambda i: layer.local_gemm(inp.x), 10, warmup=3), dev, world)
+    _sync(world)
+    ms_slabs = _max_over_ranks(time_launches(lambda i: layer.forward_slabs(inp.x), 10, warmup=3), dev, world)
+    ops = 2.0 * M * N * K
+    n_local = N // world
+    out = {
+        "ranks": world, "columns_per_rank": n_local,
+        "gemm_only_ms": round(ms_gemm, 4), "gemm_only_TOPS_whole_job": round(ops / (ms_gemm * 1e-3) / 1e12, 1),
+        "gemm_tensor_frac_per_rank": round(ops / world / (ms_gemm * 1e-3) / 1e12 / (2.0 * peaks["bf16_tflops"]), 4),
+        "quant_plus_gemm_ms": round(ms_local, 4),
+        "quant_gemm_allgather_ms": round(ms_slabs, 4),
+        "quant_gemm_allgather_TOPS_whole_job": round(ops / (ms_slabs * 1e-3) / 1e12, 1),
+    }
+    if world > 1:
+        recv = (world - 1) * M * n_local * 2
+        ag_ms = max(ms_slabs - ms_local, 1e-6)
+        out["allgather_bytes_received_per_rank"] = recv
+        out["allgather_GBps_per_rank_if_not_overlapped"] = round(recv / (ag_ms * 1e-3) / 1e9, 1)
+        out["nvlink_note"] = "measured peer copy on this pool: 770 GB/s per direction per GPU"
+    return out

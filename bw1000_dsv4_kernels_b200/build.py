@@ -48,7 +48,9 @@ def build_cuda_lib(force: bool = False, verbose: bool = False, ptxas_info: bool 
     if not force and _newer(LIB_PATH, deps):
         return LIB_PATH
     nvcc = os.path.join(_cuda_home(), "bin", "nvcc")
-    cmd = [nvcc, *ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
+    # -fmad=false: a multiply and an add that the sources write as two rounded steps must stay two
+    # instructions (fused forms are written explicitly where they are meant)
+    cmd = [nvcc, *ARCH_FLAGS, "-lineinfo", "-O3", "-fmad=false", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
            "-Xcompiler", "-fvisibility=hidden", "--threads", "4", "-o", LIB_PATH, *srcs]
     if ptxas_info:
         cmd[1:1] = ["-Xptxas", "-v"]

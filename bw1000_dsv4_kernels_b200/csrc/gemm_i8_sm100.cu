@@ -587,9 +587,11 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // and apply the channel scale once at the end of the tile.  Tile = 128 x 128.
 // ------------------------------------------------------------------------------------
 constexpr int GSN = 128;
+constexpr int kGsThreads = 320;       // producer warp, MMA warp, eight drain warps
+constexpr int kGsDrainWarps = 8;
 
 template <int STAGES>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kGsThreads, 1)
 gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const Params p) {
     using L = Smem<GSN, STAGES>;
@@ -618,7 +620,7 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(blk_full_bar(a), 1);
-            ptx::mbar_init(blk_empty_bar(a), kDrainThreads / 32);
+            ptx::mbar_init(blk_empty_bar(a), kGsDrainWarps);
         }
         *abort_flag = 0;
         ptx::fence_barrier_init();
@@ -708,8 +710,11 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
         }
     } else {
+        // Eight drain warps: warps w and w+4 share TMEM lane quarter w%4 and take 64 columns each.
+        constexpr int HC = GSN / 2;
         const int quarter = warp & 3;
-        float* sbs = sb_tile + (warp - 2) * GSN;
+        const int half = (warp - 2) >> 2;
+        float* sbs = sb_tile + quarter * GSN;  // written identically by both warps of a quarter
         const bool vec_ok = c_vector_stores_ok(p);
         uint32_t blk = 0;
         bool ok = true;
@@ -718,18 +723,33 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             __syncwarp();
             {
                 const float* sb_row = p.sb + (int64_t)c.expert * p.N;
-                for (int j = lane; j < GSN; j += 32) sbs[j] = (c.n0 + j < p.N) ? __ldg(sb_row + c.n0 + j) : 0.0f;
+                for (int j = lane; j < HC; j += 32) {
+                    const int col = half * HC + j;
+                    sbs[col] = (c.n0 + col < p.N) ? __ldg(sb_row + c.n0 + col) : 0.0f;
+                }
             }
             __syncwarp();
             const int row = c.a_row0 + quarter * 32 + lane;
             const bool row_ok = row < c.row_end;
             const float* sa_row = p.sa + (int64_t)(row_ok ? row : 0) * p.sa_groups;
-            float y[GSN];
+            // y as float2 lanes: the fold below runs on packed f32x2 instructions.  float(acc) is
+            // formed without a conversion instruction (those issue at a quarter of the FMA rate):
+            // |acc| <= 128*128*128 < 2^22, so the bit pattern 0x4B400000 + acc is the float
+            // 1.5*2^23 + acc exactly, and subtracting 1.5*2^23 leaves float(acc) exactly.
+            float2 y2[HC / 2];
 #pragma unroll
-            for (int j = 0; j < GSN; ++j) y[j] = 0.0f;
+            for (int j = 0; j < HC / 2; ++j) y2[j] = make_float2(0.0f, 0.0f);
+            // the row's group scales are fetched three K blocks ahead: a load issued in the block
+            // that needs it would expose a full L2 round trip in every block
+            float sg_a = (row_ok && 0 < k_blocks) ? __ldg(sa_row + 0) : 0.0f;
+            float sg_b = (row_ok && 1 < k_blocks) ? __ldg(sa_row + 1) : 0.0f;
+            float sg_c = (row_ok && 2 < k_blocks) ? __ldg(sa_row + 2) : 0.0f;
             for (int kb = 0; kb < k_blocks; ++kb, ++blk) {
                 const int b = blk & 1;
-                const float sg = row_ok ? __ldg(sa_row + kb) : 0.0f;
+                const float sg = sg_a;
+                sg_a = sg_b;
+                sg_b = sg_c;
+                sg_c = (row_ok && kb + 3 < k_blocks) ? __ldg(sa_row + kb + 3) : 0.0f;
                 if (!ptx::mbar_wait_bounded(blk_full_bar(b), (blk >> 1) & 1u) || *abort_flag) {
                     report_wait_failure(kWaitAccFull);
                     *abort_flag = 1;
@@ -738,34 +758,44 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 }
                 ptx::tc_fence_after_sync();
                 __syncwarp();  // tcgen05.ld is warp-collective
-                const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + b * GSN;
-#pragma unroll
-                for (int cc = 0; cc < GSN / 32; ++cc) {
-                    uint32_t r[32];
-                    ptx::tmem_ld_32x32b_x32(t_lane + cc * 32, r);
-                    ptx::tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        y[cc * 32 + j] = __fmaf_rn(__int2float_rn((int)r[j]), sg, y[cc * 32 + j]);
-                }
+                const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + b * GSN + half * HC;
+                uint32_t r0[32], r1[32];
+                ptx::tmem_ld_32x32b_x32(t_lane, r0);       // both loads in flight before the wait
+                ptx::tmem_ld_32x32b_x32(t_lane + 32, r1);
+                ptx::tmem_ld_wait();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(blk_empty_bar(b));
+                if (lane == 0) ptx::mbar_arrive(blk_empty_bar(b));  // registers hold the block now
+                const float2 sg2 = splat2(sg), unbias = splat2(-12582912.0f);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float2 f = make_float2(__int_as_float((int)r0[2 * j] + 0x4B400000),
+                                           __int_as_float((int)r0[2 * j + 1] + 0x4B400000));
+                    y2[j] = __ffma2_rn(__fadd2_rn(f, unbias), sg2, y2[j]);
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float2 f = make_float2(__int_as_float((int)r1[2 * j] + 0x4B400000),
+                                           __int_as_float((int)r1[2 * j + 1] + 0x4B400000));
+                    y2[16 + j] = __ffma2_rn(__fadd2_rn(f, unbias), sg2, y2[16 + j]);
+                }
             }
             if (!ok) break;
             if (row_ok) {
-                __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.C) + (int64_t)row * p.ldc + c.n0;
+                const int nbase = c.n0 + half * HC;
+                __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.C) + (int64_t)row * p.ldc + nbase;
+                const float* sbh = sbs + half * HC;
 #pragma unroll
-                for (int j8 = 0; j8 < GSN / 8; ++j8) {
-                    const int n = c.n0 + j8 * 8;
+                for (int j8 = 0; j8 < HC / 8; ++j8) {
+                    const int n = nbase + j8 * 8;
                     if (n >= p.N) break;
-                    const float4 s0 = *reinterpret_cast<const float4*>(sbs + j8 * 8);
-                    const float4 s1 = *reinterpret_cast<const float4*>(sbs + j8 * 8 + 4);
+                    const float4 s0 = *reinterpret_cast<const float4*>(sbh + j8 * 8);
+                    const float4 s1 = *reinterpret_cast<const float4*>(sbh + j8 * 8 + 4);
                     uint4 o;
-                    o.x = pack_bf16x2_rn(__fmul_rn(y[j8 * 8 + 0], s0.x), __fmul_rn(y[j8 * 8 + 1], s0.y));
-                    o.y = pack_bf16x2_rn(__fmul_rn(y[j8 * 8 + 2], s0.z), __fmul_rn(y[j8 * 8 + 3], s0.w));
-                    o.z = pack_bf16x2_rn(__fmul_rn(y[j8 * 8 + 4], s1.x), __fmul_rn(y[j8 * 8 + 5], s1.y));
-                    o.w = pack_bf16x2_rn(__fmul_rn(y[j8 * 8 + 6], s1.z), __fmul_rn(y[j8 * 8 + 7], s1.w));
+                    o.x = pack_bf16x2_rn(__fmul_rn(y2[j8 * 4 + 0].x, s0.x), __fmul_rn(y2[j8 * 4 + 0].y, s0.y));
+                    o.y = pack_bf16x2_rn(__fmul_rn(y2[j8 * 4 + 1].x, s0.z), __fmul_rn(y2[j8 * 4 + 1].y, s0.w));
+                    o.z = pack_bf16x2_rn(__fmul_rn(y2[j8 * 4 + 2].x, s1.x), __fmul_rn(y2[j8 * 4 + 2].y, s1.y));
+                    o.w = pack_bf16x2_rn(__fmul_rn(y2[j8 * 4 + 3].x, s1.z), __fmul_rn(y2[j8 * 4 + 3].y, s1.w));
                     if (vec_ok && n + 8 <= p.N) {
                         *reinterpret_cast<uint4*>(out + j8 * 8) = o;
                     } else {
@@ -1160,7 +1190,7 @@ int launch_gs_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Para
     if (grid <= 0) return fail(DSV4_ERR_LAUNCH, "grouped_gemm: no CUDA device");
     if (max_tiles < grid) grid = max_tiles;
     if (grid < 1) grid = 1;
-    gemm_i8_gs_kernel<STAGES><<<grid, kThreads, L::kDynamic, st>>>(tmA, tmB, p);
+    gemm_i8_gs_kernel<STAGES><<<grid, kGsThreads, L::kDynamic, st>>>(tmA, tmB, p);
     return check_launch("grouped_gemm (group-scaled)");
 }
 

@@ -1,6 +1,8 @@
 // Expert segments for the MoE grouped GEMM, computed on the device from top-k routing
 // ids: a stable counting sort by expert, written without atomics and without scratch
 // memory so that the row order inside an expert is reproducible (increasing (token, slot)).
+// Two forms with identical results: a chunked one for R >= 1024 routed pairs (below), and the
+// per-expert one described next for small inputs.
 // With expert_lo > 0 only experts [expert_lo, expert_lo + E) are sorted (expert parallelism);
 // pairs routed elsewhere get slot -1.
 //
@@ -97,6 +99,103 @@ __global__ void __launch_bounds__(kSegThreads) seg_scatter_kernel(const int* __r
     }
 }
 
+
+// ---- chunked form (R >= 1024 pairs, E <= 1024): one warp per chunk of >= 1024 pairs -----
+// count   : warp b builds the histogram of its chunk in shared memory and parks it in the
+//           chunk's own stretch of dst_slot (dst_slot[chunk_begin + e], e < E <= chunk length)
+// scan    : thread e turns the per-chunk counts of expert e into running bases (in place) and
+//           the totals into exclusive expert offsets
+// scatter : warp b reads its bases (before it overwrites that stretch), then numbers its pairs
+//           group of 32 by group of 32 in order, so rows stay sorted by (token, slot)
+// Only a chunk's own warp ever writes its stretch of dst_slot, so the parked counts cannot be
+// clobbered by another chunk; nothing outside the outputs is touched.
+constexpr int kChunk = 1024;
+
+__device__ __forceinline__ void chunk_bounds(int b, int nchunks, int R, int& lo, int& hi) {
+    lo = b * kChunk;
+    hi = (b == nchunks - 1) ? R : lo + kChunk;  // the last chunk takes the remainder as well
+}
+
+__global__ void __launch_bounds__(32) seg_chunk_count_kernel(const int* __restrict__ ids, int R, int E,
+                                                             int expert_lo, int* __restrict__ dst_slot) {
+    __shared__ int hist[1024];
+    const int lane = threadIdx.x;
+    int lo, hi;
+    chunk_bounds(blockIdx.x, gridDim.x, R, lo, hi);
+    for (int e = lane; e < E; e += 32) hist[e] = 0;
+    __syncwarp();
+    for (int i0 = lo; i0 < hi; i0 += 32) {
+        const int i = i0 + lane;
+        const int e = (i < hi) ? __ldg(ids + i) - expert_lo : -1;
+        const bool in = e >= 0 && e < E;
+        const unsigned act = __ballot_sync(0xffffffffu, in);
+        if (in) {
+            const unsigned m = __match_any_sync(act, e);
+            if (lane == __ffs(m) - 1) hist[e] += __popc(m);
+        }
+        __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32) dst_slot[lo + e] = hist[e];
+}
+
+__global__ void __launch_bounds__(1024) seg_chunk_scan_kernel(int* __restrict__ dst_slot, int nchunks, int E,
+                                                              int* __restrict__ offsets) {
+    __shared__ int totals[1024];
+    __shared__ int warp_sums[32];
+    const int e = threadIdx.x;
+    int run = 0;
+    if (e < E) {
+        for (int b = 0; b < nchunks; ++b) {
+            const int c = dst_slot[b * kChunk + e];
+            dst_slot[b * kChunk + e] = run;  // rows of expert e that earlier chunks contribute
+            run += c;
+        }
+    }
+    totals[e] = (e < E) ? run : 0;
+    // exclusive scan of the totals over the experts
+    const int lane = e & 31, warp = e >> 5;
+    int incl = warp_incl_scan(totals[e], lane);
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const int ws = warp_sums[lane];
+        const int wi = warp_incl_scan(ws, lane);
+        warp_sums[lane] = wi - ws;
+    }
+    __syncthreads();
+    const int excl = warp_sums[warp] + incl - totals[e];
+    if (e < E) offsets[e] = excl;
+    if (e == E - 1) offsets[E] = excl + totals[e];
+}
+
+__global__ void __launch_bounds__(32) seg_chunk_scatter_kernel(const int* __restrict__ ids, int R, int topk, int E,
+                                                               int expert_lo, const int* __restrict__ offsets,
+                                                               int* __restrict__ src_row, int* __restrict__ dst_slot) {
+    __shared__ int base[1024];
+    const int lane = threadIdx.x;
+    int lo, hi;
+    chunk_bounds(blockIdx.x, gridDim.x, R, lo, hi);
+    for (int e = lane; e < E; e += 32) base[e] = offsets[e] + dst_slot[lo + e];
+    __syncwarp();
+    for (int i0 = lo; i0 < hi; i0 += 32) {
+        const int i = i0 + lane;
+        const int e = (i < hi) ? __ldg(ids + i) - expert_lo : -1;
+        const bool in = e >= 0 && e < E;
+        const unsigned act = __ballot_sync(0xffffffffu, in);
+        if (in) {
+            const unsigned m = __match_any_sync(act, e);
+            const int r = base[e] + __popc(m & ((1u << lane) - 1u));
+            src_row[r] = i / topk;
+            dst_slot[i] = r;
+            __syncwarp(m);
+            if (lane == __ffs(m) - 1) base[e] += __popc(m);
+        } else if (i < hi) {
+            dst_slot[i] = -1;
+        }
+        __syncwarp();
+    }
+}
+
 __global__ void __launch_bounds__(128) gather_rows_kernel(const uint4* __restrict__ src,
                                                           const int* __restrict__ src_row,
                                                           uint4* __restrict__ dst, int R, int vec_per_row,
@@ -179,6 +278,13 @@ int moe_segments(const int* topk_ids, int T, int topk, int E, int expert_lo, int
     const int64_t R64 = (int64_t)T * topk;
     if (R64 > INT32_MAX) return fail(DSV4_ERR_ARG, "moe_segments: T*topk exceeds int32");
     const int R = (int)R64;
+    if (R >= kChunk && E <= 1024) {
+        const int nchunks = R / kChunk;
+        seg_chunk_count_kernel<<<nchunks, 32, 0, st>>>(topk_ids, R, E, expert_lo, dst_slot);
+        seg_chunk_scan_kernel<<<1, 1024, 0, st>>>(dst_slot, nchunks, E, offsets);
+        seg_chunk_scatter_kernel<<<nchunks, 32, 0, st>>>(topk_ids, R, topk, E, expert_lo, offsets, src_row, dst_slot);
+        return check_launch("moe_segments");
+    }
     seg_count_kernel<<<E, kSegThreads, 0, st>>>(topk_ids, R, expert_lo, offsets, dst_slot);
     seg_scan_kernel<<<1, 32, 0, st>>>(offsets, E);
     seg_scatter_kernel<<<E, kSegThreads, 0, st>>>(topk_ids, R, topk, expert_lo, offsets, src_row, dst_slot);

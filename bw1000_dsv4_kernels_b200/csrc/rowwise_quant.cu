@@ -170,14 +170,15 @@ __global__ void __launch_bounds__(256) ptgq_vec_kernel(const uint4* __restrict__
             for (int o = LPG / 2; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
             if (f < nvec) {
                 const float scale = __fdiv_rn(fmaxf(am, kAmaxFloor), 127.0f);
+                const float rcp = __frcp_rn(scale);
                 if ((threadIdx.x & (LPG - 1)) == 0) s[f / LPG] = scale;
                 float e[8];
                 unpack8(v[u], e);
                 uint2 o2;
-                o2.x = pack_i8x4(quant_trunc_div(e[0], scale), quant_trunc_div(e[1], scale),
-                                 quant_trunc_div(e[2], scale), quant_trunc_div(e[3], scale));
-                o2.y = pack_i8x4(quant_trunc_div(e[4], scale), quant_trunc_div(e[5], scale),
-                                 quant_trunc_div(e[6], scale), quant_trunc_div(e[7], scale));
+                o2.x = pack_i8x4(quant_trunc_div_rcp(e[0], scale, rcp), quant_trunc_div_rcp(e[1], scale, rcp),
+                                 quant_trunc_div_rcp(e[2], scale, rcp), quant_trunc_div_rcp(e[3], scale, rcp));
+                o2.y = pack_i8x4(quant_trunc_div_rcp(e[4], scale, rcp), quant_trunc_div_rcp(e[5], scale, rcp),
+                                 quant_trunc_div_rcp(e[6], scale, rcp), quant_trunc_div_rcp(e[7], scale, rcp));
                 q[f] = o2;
             }
         }
@@ -457,6 +458,75 @@ __global__ void __launch_bounds__(T, MINB) silu_mul_quant_vec_kernel(
     }
 }
 
+// Persistent form for many rows: a CTA first tabulates the sigmoid of every bf16 gate value in
+// [2^-12, 16) (both signs) in shared memory, then walks rows blockIdx.x, +gridDim.x, ...  The
+// per-element work drops from ~30 to ~15 issue slots, which is what lets the kernel run at
+// memory speed.  Shared memory: N floats for the row, then the 16 KB table.
+template <int T, int MINB>
+__global__ void __launch_bounds__(T, MINB) silu_mul_quant_table_kernel(
+    const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
+    const int* __restrict__ mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
+    float* __restrict__ s, int M, int N, int64_t ldg, int64_t ldu) {
+    extern __shared__ float4 h_row4[];
+    __shared__ float red[32];
+    float* tab = reinterpret_cast<float*>(h_row4) + N;
+    const int V = N >> 3, tid = threadIdx.x;
+    if (valid_rows != nullptr) M = min(M, __ldg(valid_rows));
+    if ((int)blockIdx.x >= M) return;
+    for (int i = tid; i < kSigTabEntries; i += T) tab[i] = sigmoid_table_entry(i);
+    __syncthreads();
+    for (int row = blockIdx.x; row < M; row += gridDim.x) {
+        if (mask != nullptr && mask[row] == 0) continue;  // uniform over the block
+        const uint4* gr = reinterpret_cast<const uint4*>(g + (int64_t)row * ldg);
+        const uint4* ur = reinterpret_cast<const uint4*>(u + (int64_t)row * ldu);
+        float am = 0.0f;
+        constexpr int NB = 3;  // vectors of each operand in flight per thread
+        for (int base = tid; base < V; base += NB * T) {
+            uint4 gv[NB], uv[NB];
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                const int idx = base + j * T;
+                if (idx < V) {
+                    gv[j] = ld_stream(gr + idx);
+                    uv[j] = ld_stream(ur + idx);
+                } else {
+                    gv[j] = make_uint4(0, 0, 0, 0);
+                    uv[j] = gv[j];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                const int idx = base + j * T;
+                if (idx >= V) break;
+                float2 h[4];
+                silu_mul8_table(gv[j], uv[j], tab, h);
+                am = fmaxf(am, fmaxf(fmaxf(fabsf(h[0].x), fabsf(h[0].y)), fmaxf(fabsf(h[1].x), fabsf(h[1].y))));
+                am = fmaxf(am, fmaxf(fmaxf(fabsf(h[2].x), fabsf(h[2].y)), fmaxf(fabsf(h[3].x), fabsf(h[3].y))));
+                h_row4[2 * idx] = make_float4(h[0].x, h[0].y, h[1].x, h[1].y);
+                h_row4[2 * idx + 1] = make_float4(h[2].x, h[2].y, h[3].x, h[3].y);
+            }
+        }
+        am = block_max(am, red);
+        float scale, inv;
+        scale_from_amax(am, scale, inv);
+        if (tid == 0) s[row] = scale;
+        const float2 inv2 = splat2(inv);
+        uint2* qr = reinterpret_cast<uint2*>(q + (int64_t)row * N);
+        for (int idx = tid; idx < V; idx += T) {
+            const float4 a = h_row4[2 * idx], b = h_row4[2 * idx + 1];
+            const float2 c0 = quant_rn_lowbyte2(make_float2(a.x, a.y), inv2);
+            const float2 c1 = quant_rn_lowbyte2(make_float2(a.z, a.w), inv2);
+            const float2 c2 = quant_rn_lowbyte2(make_float2(b.x, b.y), inv2);
+            const float2 c3 = quant_rn_lowbyte2(make_float2(b.z, b.w), inv2);
+            uint2 o;
+            o.x = pack_lowbytes(__float_as_uint(c0.x), __float_as_uint(c0.y), __float_as_uint(c1.x), __float_as_uint(c1.y));
+            o.y = pack_lowbytes(__float_as_uint(c2.x), __float_as_uint(c2.y), __float_as_uint(c3.x), __float_as_uint(c3.y));
+            qr[idx] = o;
+        }
+        __syncthreads();
+    }
+}
+
 __global__ void __launch_bounds__(256) silu_mul_quant_generic_kernel(
     const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
     const int* __restrict__ mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
@@ -653,6 +723,23 @@ int silu_mul_quant(const void* g, const void* u, const int* mask, const int* val
             cudaFuncSetAttribute(silu_mul_quant_vec_kernel<256, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
             cudaFuncSetAttribute(silu_mul_quant_vec_kernel<384, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
             if (dev >= 0 && dev < 64) opted_in[dev] = true;
+        }
+        const size_t tab_smem = row_smem + kSigTabEntries * sizeof(float);
+        int sms = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms > 0 && M >= 4 * sms && tab_smem <= 110 * 1024) {
+            // many rows: persistent CTAs (two per SM) with the sigmoid table
+            static bool tab_opted_in[64] = {};
+            if (dev < 0 || dev >= 64 || !tab_opted_in[dev]) {
+                cudaFuncSetAttribute(silu_mul_quant_table_kernel<512, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+                cudaFuncSetAttribute(silu_mul_quant_table_kernel<256, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+                if (dev >= 0 && dev < 64) tab_opted_in[dev] = true;
+            }
+            if (V > 512)
+                silu_mul_quant_table_kernel<512, 2><<<2 * sms, 512, tab_smem, st>>>(gp, up, mask, valid_rows, qp, sp, M, N, ldg, ldu);
+            else
+                silu_mul_quant_table_kernel<256, 4><<<4 * sms, 256, tab_smem, st>>>(gp, up, mask, valid_rows, qp, sp, M, N, ldg, ldu);
+            return check_launch("silu_mul_quant");
         }
         if (V <= 256)
             silu_mul_quant_vec_kernel<128, 8><<<grid_rows(M), 128, row_smem, st>>>(gp, up, mask, valid_rows, qp, sp, M, N, ldg, ldu);

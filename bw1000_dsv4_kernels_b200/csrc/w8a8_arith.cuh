@@ -72,6 +72,18 @@ __device__ __forceinline__ int quant_trunc_div(float x, float scale) {
     return __float2int_rz(t);
 }
 
+// The same quotient without a division per element: with rcp = RN(1/scale) computed once per
+// group, q0 = RN(x*rcp), r = fma(-q0, scale, x) (the exact residual, rounded once) and
+// q1 = fma(r, rcp, q0) is the correctly rounded x/scale for operands in the normal range
+// (the final step of the standard division algorithm); below 1 in magnitude the truncation is
+// zero whatever the last bit.  Checked against true division in the GPU tests.
+__device__ __forceinline__ int quant_trunc_div_rcp(float x, float scale, float rcp) {
+    const float q0 = __fmul_rn(x, rcp);
+    const float r = __fmaf_rn(-q0, scale, x);
+    const float q1 = __fmaf_rn(r, rcp, q0);
+    return max(-128, min(127, __float2int_rz(q1)));
+}
+
 __device__ __forceinline__ uint32_t pack_i8x4(int a, int b, int c, int d) {
     return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) |
            ((uint32_t)(d & 0xff) << 24);
@@ -111,11 +123,36 @@ __device__ __forceinline__ float exp_fixed(float x) {
     return __int_as_float(__float_as_int(p) + (__float_as_int(z) << 23));
 }
 
+// sigmoid(g) = 1/(1+exp(-g)); __frcp_rn is the correctly rounded reciprocal == IEEE 1.0f / x
+__device__ __forceinline__ float sigmoid_fixed(float g) {
+    return __frcp_rn(__fadd_rn(1.0f, exp_fixed(-g)));
+}
+
 // h = ((1/(1+exp(-g))) * g) * u, each step rounded to f32
 __device__ __forceinline__ float silu_mul(float g, float u) {
-    float e = exp_fixed(-g);
-    float sig = __frcp_rn(__fadd_rn(1.0f, e));  // correctly rounded reciprocal == IEEE 1.0f / x
-    return __fmul_rn(__fmul_rn(sig, g), u);
+    return __fmul_rn(__fmul_rn(sigmoid_fixed(g), g), u);
+}
+
+// ---- sigmoid by table -------------------------------------------------------------------
+// The gate is bf16: only 65536 inputs exist.  A kernel may tabulate sigmoid_fixed for the
+// inputs with 2^-12 <= |g| < 16 (2048 bit patterns per sign, 4096 floats = 16 KB of shared
+// memory) and look values up instead of recomputing them; inputs outside that range (zeros,
+// tiny, huge, NaN) take sigmoid_fixed directly.  The table holds sigmoid_fixed's own results,
+// so a lookup returns exactly what the computation would.
+constexpr uint32_t kSigTabLo = 0x3980u;    // bf16 bits of 2^-12
+constexpr int kSigTabEntries = 4096;       // [sign][(|g| bits) - kSigTabLo]
+
+__device__ __forceinline__ float sigmoid_table_entry(int i) {
+    const uint32_t bits = ((uint32_t)(i >> 11) << 15) | (kSigTabLo + (uint32_t)(i & 0x7ff));
+    return sigmoid_fixed(__uint_as_float(bits << 16));
+}
+
+// Index arithmetic: t = (bf16 bits - kSigTabLo) mod 2^16 is a table hit iff bits 11..14 are
+// clear (bit 15 is the sign); the entry is (t & 0x7ff) | (sign << 11).
+__device__ __forceinline__ uint32_t sig_t_lo(uint32_t gw) { return (gw - kSigTabLo) & 0xffffu; }
+__device__ __forceinline__ uint32_t sig_t_hi(uint32_t gw) { return ((gw >> 16) - kSigTabLo) & 0xffffu; }
+__device__ __forceinline__ float sig_entry(uint32_t t, const float* __restrict__ tab) {
+    return tab[(t & 0x7ffu) | ((t >> 4) & 0x800u)];
 }
 
 // ---- two-lane forms ------------------------------------------------------------------
@@ -152,9 +189,45 @@ __device__ __forceinline__ float2 silu_mul2(float2 g, float2 u) {
     return __fmul2_rn(__fmul2_rn(sig, g), u);
 }
 
-// int8 codes of two values in the low bytes of the two returned words (see quant_rn_lowbyte)
+// int8 codes of two values in the low bytes of the two returned words (see quant_rn_lowbyte).
+// The product must be rounded before the add (x*inv can land exactly on a half after rounding and
+// then rounds to even; a fused multiply-add would round the unrounded product instead), so the
+// two steps are pinned as separate instructions.
 __device__ __forceinline__ float2 quant_rn_lowbyte2(float2 x, float2 inv2) {
-    return __fadd2_rn(__fmul2_rn(x, inv2), splat2(kRoundMagic));
+    unsigned long long xi, ii, mi, prod, sum;
+    const float2 magic = splat2(kRoundMagic);
+    xi = *reinterpret_cast<const unsigned long long*>(&x);
+    ii = *reinterpret_cast<const unsigned long long*>(&inv2);
+    mi = *reinterpret_cast<const unsigned long long*>(&magic);
+    asm volatile("mul.rn.f32x2 %0, %1, %2;" : "=l"(prod) : "l"(xi), "l"(ii));
+    asm volatile("add.rn.f32x2 %0, %1, %2;" : "=l"(sum) : "l"(prod), "l"(mi));
+    return *reinterpret_cast<float2*>(&sum);
+}
+
+// h for the 8 gates / ups of one 16-byte vector pair.  One range test for the whole vector: if
+// all 8 gates hit the table the values are looked up, otherwise (rare: zeros, tiny or huge
+// gates) the whole vector is computed.  Both give sigmoid_fixed's value.
+__device__ __forceinline__ void silu_mul8_table(const uint4& gv, const uint4& uv, const float* __restrict__ tab,
+                                                float2 (&h)[4]) {
+    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+    uint32_t t[8];
+    uint32_t miss = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        t[2 * i] = sig_t_lo(gw[i]);
+        t[2 * i + 1] = sig_t_hi(gw[i]);
+        miss |= t[2 * i] | t[2 * i + 1];
+    }
+    if ((miss & 0x7800u) == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 sig = make_float2(sig_entry(t[2 * i], tab), sig_entry(t[2 * i + 1], tab));
+            h[i] = __fmul2_rn(__fmul2_rn(sig, bf16x2_to_f32x2(gw[i])), bf16x2_to_f32x2(uw[i]));
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = silu_mul2(bf16x2_to_f32x2(gw[i]), bf16x2_to_f32x2(uw[i]));
+    }
 }
 
 // rrms = 1 / sqrt(sumsq / n + eps)

@@ -194,3 +194,63 @@ def test_silu_mul_masked_quant(cabi, ext):
     q2, s2 = ext.silu_mul_masked_quant(gud[:, :n], gud[:, n:], mask.cuda())
     _eq(q2, q_ref, "codes (operator)")
     _eq(s2, s_ref, "scales (operator)")
+
+
+@pytest.mark.parametrize("m,n", [(640, 18432), (1500, 2048), (600, 520)])
+def test_silu_mul_quant_many_rows_table_path(cabi, ext, m, n):
+    # enough rows for the persistent kernel that looks sigmoid up in a shared-memory table; the
+    # inputs include values outside the table's range (zeros, denormal-small, huge, both signs)
+    gu = wl.randn_bf16((m, 2 * n), seed=m + n)
+    special = torch.tensor([0.0, -0.0, 1e-6, -1e-6, 2.0 ** -12, -(2.0 ** -12), 2.0 ** -13, 15.9375, 16.0, -16.0,
+                            -15.9375, 90.0, -90.0, 1e30, -1e30, 1e-30], dtype=torch.float32).bfloat16()
+    gu[0, :special.numel()] = special
+    gu[m - 1, n - special.numel():n] = special
+    gu[1] = 0.0                                    # an all-zero row
+    q_ref, s_ref = oracle.silu_mul_quant(gu[:, :n], gu[:, n:])
+    gud = gu.cuda()
+    q, s = cabi.silu_mul_quant(gud[:, :n], gud[:, n:])
+    _eq(s, s_ref, "scales")
+    _eq(q, q_ref, "codes")
+    q2, s2 = ext.silu_mul_quant(gud[:, :n], gud[:, n:])
+    _eq(q2, q_ref, "codes (operator)")
+    _eq(s2, s_ref, "scales (operator)")
+
+
+def test_sigmoid_table_covers_every_bf16_gate(cabi):
+    # every one of the 65536 bf16 bit patterns as a gate (NaNs excluded), up = 1: the table path and
+    # the computed path must agree with the oracle for all of them
+    bits = torch.arange(0, 65536, dtype=torch.int32)
+    finite = (bits & 0x7F80) != 0x7F80
+    g = bits[finite].to(torch.int16).view(torch.bfloat16)
+    n = 1024
+    rows = 640
+    pad = rows * n - g.numel()
+    g_all = torch.cat([g, g[:pad]]).view(rows, n).contiguous()
+    u_all = torch.ones_like(g_all)
+    q_ref, s_ref = oracle.silu_mul_quant(g_all, u_all)
+    q, s = cabi.silu_mul_quant(g_all.cuda(), u_all.cuda())
+    _eq(s, s_ref, "scales")
+    _eq(q, q_ref, "codes")
+
+
+def test_ptgq_many_elements_and_exact_multiples(cabi):
+    # the vector kernel replaces the per-element division by a reciprocal and one correction step;
+    # 29 M random elements plus rows built from exact multiples of the scale (quotients that are
+    # integers or sit next to one) must still truncate exactly like true division
+    x = wl.activations_with_outliers(4096, 7168, seed=123)
+    q_ref, s_ref = oracle.per_token_group_quant_int8(x, 128)
+    q, s = cabi.ptgq(x.cuda(), 128)
+    _eq(s, s_ref, "scales")
+    _eq(q, q_ref, "codes")
+    k = torch.arange(-127, 129, dtype=torch.float32)[:256]
+    rows = []
+    for amax in (127.0, 1.0, 3.0, 0.4375, 100.0, 254.0, 1e-3, 7.0):
+        base = (k[:128] * (amax / 127.0)).bfloat16().float()
+        base[0] = amax
+        rows.append(base)
+        rows.append((-k[128:] * (amax / 127.0)).bfloat16().float().clone().index_fill_(0, torch.tensor([0]), -amax))
+    xm = torch.stack(rows).bfloat16()
+    q_ref, s_ref = oracle.per_token_group_quant_int8(xm, 128)
+    q, s = cabi.ptgq(xm.cuda(), 128)
+    _eq(s, s_ref, "scales (multiples)")
+    _eq(q, q_ref, "codes (multiples)")
