@@ -327,24 +327,57 @@ def run_ours(args):
                                                                     sets[i % nsets].w_scale))
 
         # ---- end to end through the operator module with host buffers --------------------
-        e2e_steps = max(3, min(args.steps, 30))
+        # Every step copies its x and res from pinned host memory, runs the two operators and copies
+        # the output and the updated residual back.  Three streams and two sets of device buffers
+        # let step i+1's upload and step i-1's download overlap step i's kernels (PCIe is full
+        # duplex); the timed region still contains every copy of every step.
+        e2e_steps = max(4, min(args.steps, 40))
         hx = sets[0].x.cpu().pin_memory()
         hres = sets[0].res.cpu().pin_memory()
-        hout = torch.empty((M_ROWS, N_DIM), dtype=torch.bfloat16).pin_memory()
-        hres_out = torch.empty((M_ROWS, K_DIM), dtype=torch.bfloat16).pin_memory()
-        dx = torch.empty_like(sets[0].x)
-        dres = torch.empty_like(sets[0].res)
+        houts = [torch.empty((M_ROWS, N_DIM), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        hres_outs = [torch.empty((M_ROWS, K_DIM), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        dxs = [torch.empty_like(sets[0].x) for _ in range(2)]
+        dress = [torch.empty_like(sets[0].res) for _ in range(2)]
+        s_in, s_comp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_comp = [torch.cuda.Event() for _ in range(2)]
+        ev_out = [torch.cuda.Event() for _ in range(2)]
+        keep = [None, None]
 
-        def e2e_step(i):
-            dx.copy_(hx, non_blocking=True)
-            dres.copy_(hres, non_blocking=True)
-            q, sc = ext.add_rmsnorm_quant(dres, dx, gamma, 1e-6)
-            out = ext.w8a8_scaled_gemm(q, sets[i % nsets].w, sc, sets[i % nsets].w_scale)
-            hout.copy_(out, non_blocking=True)
-            hres_out.copy_(dres, non_blocking=True)
+        def e2e_run(n_steps):
+            for i in range(n_steps):
+                b = i & 1
+                with torch.cuda.stream(s_in):
+                    s_in.wait_event(ev_out[b])          # buffer b's previous download has finished
+                    dxs[b].copy_(hx, non_blocking=True)
+                    dress[b].copy_(hres, non_blocking=True)
+                    ev_in[b].record(s_in)
+                with torch.cuda.stream(s_comp):
+                    s_comp.wait_event(ev_in[b])
+                    q, sc = ext.add_rmsnorm_quant(dress[b], dxs[b], gamma, 1e-6)
+                    out = ext.w8a8_scaled_gemm(q, sets[i % nsets].w, sc, sets[i % nsets].w_scale)
+                    keep[b] = (q, sc, out)
+                    ev_comp[b].record(s_comp)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_comp[b])
+                    houts[b].copy_(out, non_blocking=True)
+                    hres_outs[b].copy_(dress[b], non_blocking=True)
+                    ev_out[b].record(s_out)
 
+        cur = torch.cuda.current_stream()
+        e2e_run(4)
+        torch.cuda.synchronize()
         barrier()
-        ms_e2e = time_launches(e2e_step, e2e_steps, warmup=2)
+        e2e_start, e2e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2e_start.record(cur)
+        for st_ in (s_in, s_comp, s_out):
+            st_.wait_event(e2e_start)
+        e2e_run(e2e_steps)
+        for st_ in (s_in, s_comp, s_out):
+            cur.wait_stream(st_)
+        e2e_end.record(cur)
+        e2e_end.synchronize()
+        ms_e2e = e2e_start.elapsed_time(e2e_end) / e2e_steps
         if world > 1:
             t = torch.tensor([ms_e2e], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -389,7 +422,10 @@ def run_ours(args):
                                   "frac": quant_gbs / peaks["hbm_gbs"], "launch_us": ms_quant * 1e3,
                                   "bytes": quant_bytes_add_rmsnorm(M_ROWS, K_DIM)},
         },
-        "e2e": {"value": e2e_value, "unit": "TOPS", "ms_per_step": ms_e2e,
+        "e2e": {"value": e2e_value, "unit": "TOPS", "ms_per_step": ms_e2e, "steps": e2e_steps,
+                "how": "pinned host -> device copies of x and res, add_rmsnorm_quant, w8a8_scaled_gemm, device -> host "
+                       "copies of the output and the updated residual, every step; upload / kernels / download of "
+                       "neighbouring steps overlap on three streams",
                 "h2d_bytes_per_step": 2 * M_ROWS * K_DIM * 2, "d2h_bytes_per_step": M_ROWS * N_DIM * 2 + M_ROWS * K_DIM * 2},
         "gpu_launches": 2 * args.steps,
         "clocks": sampler.summary(),

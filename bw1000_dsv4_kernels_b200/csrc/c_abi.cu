@@ -183,6 +183,19 @@ int launch_moe_combine(const void* z, const int* dst_slot, const float* topk_w, 
     return moe_combine(z, dst_slot, topk_w, out, T, topk, H, out_f32, cs(stream));
 }
 
+int launch_w8a8_gemm_allgather(const void* A, const void* B, const void* sa, const void* sb, void* C_local,
+                               void* const* C_peers, int npeers, int64_t ldc, int M, int N, int K,
+                               dsv4_stream_t stream) {
+    if (npeers < 0 || npeers > 7) return fail(DSV4_ERR_ARG, "w8a8_gemm_allgather: npeers must be in 0..7");
+    if (npeers > 0 && C_peers == nullptr) return fail(DSV4_ERR_ARG, "w8a8_gemm_allgather: null pointer C_peers");
+    GemmArgs a{};
+    a.A = A; a.B = B; a.sa = static_cast<const float*>(sa); a.sb = static_cast<const float*>(sb); a.C = C_local;
+    a.offsets = nullptr; a.M = M; a.N = N; a.K = K; a.E = 1; a.ldc = ldc; a.sa_groups = 1; a.out_i32 = 0;
+    a.npeers = npeers;
+    for (int d = 0; d < npeers; ++d) a.peerC[d] = C_peers[d];
+    return gemm_i8(a, cs(stream));
+}
+
 int launch_w8a8_gemm_ld(const void* A, const void* B, const void* sa, const void* sb, void* C, int64_t ldc, int M,
                         int N, int K, dsv4_stream_t stream) {
     GemmArgs a{};

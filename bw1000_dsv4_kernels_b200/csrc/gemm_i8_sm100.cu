@@ -61,6 +61,10 @@ struct Params {
     int64_t ldc;         // row stride of C in elements (>= N)
     int sa_groups;
     int out_i32;
+    // Fused all-gather: besides C, every output tile is also stored to these buffers (the same
+    // slab of the other ranks' outputs, mapped into this process); same ldc.  npeers = 0: none.
+    void* peerC[7];
+    int npeers;
 };
 
 template <int BN, int STAGES>
@@ -186,6 +190,14 @@ __device__ __forceinline__ void drain_accumulator(const Params& p, uint32_t t_la
                 for (int j = 0; j < 4; ++j)
                     *reinterpret_cast<uint4*>(out + 8 * j) =
                         make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                // the same 64 bytes to every peer's copy of the output (plain stores over NVLink)
+                for (int d = 0; d < p.npeers; ++d) {
+                    __nv_bfloat16* po = static_cast<__nv_bfloat16*>(p.peerC[d]) + (int64_t)row * p.ldc + n;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        *reinterpret_cast<uint4*>(po + 8 * j) =
+                            make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                }
             } else {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
@@ -1240,6 +1252,20 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
     p.ldc = a.ldc > 0 ? a.ldc : a.N;
     p.sa_groups = a.sa_groups; p.out_i32 = a.out_i32;
     if (p.ldc < a.N) return fail(DSV4_ERR_ARG, "w8a8_gemm: ldc smaller than N");
+    p.npeers = 0;
+    for (int d = 0; d < 7; ++d) p.peerC[d] = nullptr;
+    if (a.npeers > 0) {
+        if (a.npeers > 7 || grouped || a.out_i32 || a.sa_groups != 1)
+            return fail(DSV4_ERR_ARG, "w8a8_gemm_allgather: at most 7 peers, dense per-token-scaled bf16 output only");
+        if (a.N % 32 != 0 || p.ldc % 8 != 0 || (reinterpret_cast<uintptr_t>(a.C) & 15))
+            return fail(DSV4_ERR_ARG, "w8a8_gemm_allgather: N % 32 == 0, ldc % 8 == 0 and 16-byte aligned outputs required");
+        for (int d = 0; d < a.npeers; ++d) {
+            if (a.peerC[d] == nullptr || (reinterpret_cast<uintptr_t>(a.peerC[d]) & 15))
+                return fail(DSV4_ERR_ARG, "w8a8_gemm_allgather: null or misaligned peer pointer");
+            p.peerC[d] = a.peerC[d];
+        }
+        p.npeers = a.npeers;
+    }
 
     const uint64_t b_rows = grouped ? (uint64_t)a.E * a.N : (uint64_t)a.N;
     const int sms = sm_count();
@@ -1261,7 +1287,7 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
         return launch_gs_variant<6>(tmA, tmB, p, tiles_m_bound * ((a.N + GSN - 1) / GSN), st);
     }
     // Few tokens: stream the weight once, tokens on the MMA's N axis, K split over a cluster
-    if (!grouped && a.M <= 256) {
+    if (!grouped && a.M <= 256 && a.npeers == 0) {
         const int n_tiles = (a.N + 127) / 128;
         const int k_blocks = (a.K + BK - 1) / BK;
         int splits = sms / n_tiles;

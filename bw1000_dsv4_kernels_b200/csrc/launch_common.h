@@ -35,6 +35,8 @@ struct GemmArgs {
     int64_t ldc;          // row stride of C in elements; 0 = N
     int sa_groups;        // 1 = per-token scale; K/128 = one scale per 128 of K
     int out_i32;          // 1 = write raw int32 accumulators
+    void* peerC[7];       // fused all-gather: the other ranks' mapped output slabs
+    int npeers;           // 0 = none
 };
 int gemm_i8(const GemmArgs& a, cudaStream_t st);
 int scale_convert(const void* acc, const void* sa, const void* sb, void* out, int M, int N,

@@ -607,18 +607,17 @@ int ptq(const void* x, void* q, void* s, int M, int K, int64_t ldx, cudaStream_t
     auto sp = static_cast<float*>(s);
     const bool vec = (K % 8 == 0) && (ldx % 8 == 0) && aligned16(x) && ((reinterpret_cast<uintptr_t>(q) & 7) == 0);
     const int V = K / 8;
-    if (vec && V <= 4 * 1024) {
-        if (V <= 1024) {  // one vector per thread up to 8192 columns
-            int T = round_up32(V);
-            if (V > 512) {
-                ptq_vec_kernel<2><<<grid_rows(M), round_up32((V + 1) / 2), 0, st>>>(xp, qp, sp, M, K, ldx);
-            } else {
-                ptq_vec_kernel<1><<<grid_rows(M), T < 64 ? 64 : T, 0, st>>>(xp, qp, sp, M, K, ldx);
-            }
-        } else if (V <= 2048) {
-            ptq_vec_kernel<2><<<grid_rows(M), round_up32((V + 1) / 2), 0, st>>>(xp, qp, sp, M, K, ldx);
-        } else {
-            ptq_vec_kernel<4><<<grid_rows(M), round_up32((V + 3) / 4), 0, st>>>(xp, qp, sp, M, K, ldx);
+    if (vec && V <= 8 * 1024) {
+        // vectors per thread: the smallest of 1,2,4,8 that keeps the CTA at 256 threads or fewer
+        // (small CTAs -> many resident rows per SM, several 16-byte loads in flight per thread)
+        const int vpt = V <= 256 ? 1 : V <= 512 ? 2 : V <= 1024 ? 4 : 8;
+        int T = round_up32((V + vpt - 1) / vpt);
+        if (T < 64) T = 64;
+        switch (vpt) {
+            case 1: ptq_vec_kernel<1><<<grid_rows(M), T, 0, st>>>(xp, qp, sp, M, K, ldx); break;
+            case 2: ptq_vec_kernel<2><<<grid_rows(M), T, 0, st>>>(xp, qp, sp, M, K, ldx); break;
+            case 4: ptq_vec_kernel<4><<<grid_rows(M), T, 0, st>>>(xp, qp, sp, M, K, ldx); break;
+            default: ptq_vec_kernel<8><<<grid_rows(M), T, 0, st>>>(xp, qp, sp, M, K, ldx); break;
         }
     } else {
         ptq_generic_kernel<<<grid_rows(M), 256, 0, st>>>(xp, qp, sp, M, K, ldx);

@@ -364,6 +364,27 @@ void w8a8_gemm_into_stream(Tensor A, Tensor B, Tensor sa, Tensor sb, Tensor out,
                                      g.M, g.N, g.K, as_stream(stream_ptr)));
 }
 
+// Fused GEMM + all-gather: the result goes to columns [col0, col0+N) of `out` and of every buffer
+// whose base address is listed in peer_ptrs (device pointers to the other ranks' [M, ldc] outputs,
+// e.g. torch.distributed._symmetric_memory buffer_ptrs), all with out's row stride.
+void w8a8_gemm_allgather_stream(Tensor A, Tensor B, Tensor sa, Tensor sb, Tensor out, int64_t col0,
+                                std::vector<int64_t> peer_ptrs, int64_t stream_ptr) {
+    const GemmShape g = check_gemm_operands(A, B);
+    auto sa_c = flat_scale(sa, g.M, "sa");
+    auto sb_c = flat_scale(sb, g.N, "sb");
+    check_cuda(out, "out", torch::kBFloat16);
+    TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1 && out.size(0) == g.M && col0 >= 0 && col0 + g.N <= out.size(1),
+                "out must be a [M, >= col0 + N] bf16 tensor with unit inner stride");
+    TORCH_CHECK(peer_ptrs.size() <= 7, "at most 7 peers");
+    c10::cuda::CUDAGuard guard(A.device());
+    std::vector<void*> peers;
+    for (int64_t ptr : peer_ptrs) peers.push_back(reinterpret_cast<at::BFloat16*>(ptr) + col0);
+    auto* base = static_cast<at::BFloat16*>(out.data_ptr()) + col0;
+    check_status(launch_w8a8_gemm_allgather(A.data_ptr(), B.data_ptr(), sa_c.data_ptr(), sb_c.data_ptr(), base,
+                                            peers.data(), (int)peers.size(), out.stride(0), g.M, g.N, g.K,
+                                            as_stream(stream_ptr)));
+}
+
 int64_t device_status() {
     int v = 0;
     check_status(dsv4_device_status(as_stream(current_stream_ptr()), &v));
@@ -434,6 +455,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         w8a8_gemm_into_stream(A, B, sa, sb, out, col0, current_stream_ptr());
     });
     m.def("w8a8_gemm_into_stream", &w8a8_gemm_into_stream);
+    m.def("w8a8_gemm_allgather", [](Tensor A, Tensor B, Tensor sa, Tensor sb, Tensor out, int64_t col0,
+                                    std::vector<int64_t> peers) {
+        w8a8_gemm_allgather_stream(A, B, sa, sb, out, col0, peers, current_stream_ptr());
+    });
+    m.def("w8a8_gemm_allgather_stream", &w8a8_gemm_allgather_stream);
     m.def("device_status", &device_status);
     m.def("abi_version", [] { return dsv4_abi_version(); });
 }

@@ -65,3 +65,35 @@ class ColumnParallelW8A8Linear:
         if self.world == 1:
             return slabs[0]
         return slabs.permute(1, 0, 2).reshape(x.shape[0], self.world * self.n_local)
+
+
+class FusedColumnParallelW8A8Linear(ColumnParallelW8A8Linear):
+    """Same layer with the exchange fused into the GEMM: the output [M, N] lives in symmetric
+    memory (every rank's buffer is mapped into every other rank), and the GEMM's tile epilogue
+    stores each piece of this rank's column slab into all G buffers with plain stores over NVLink
+    (`w8a8_gemm_allgather`), so the transfer overlaps the tensor-core work tile by tile and the
+    result is row-major without a gather or a permute.  A symmetric-memory barrier on the stream
+    before the kernel keeps a rank from overwriting rows a slower peer is still reading from the
+    previous call, and one after it makes every slab visible before anyone reads a full row."""
+
+    def __init__(self, w_local, w_scale_local, rank, world, m_max, device, process_group=None):
+        super().__init__(w_local, w_scale_local, rank, world, process_group)
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        self.n = self.n_local * world
+        self._symm = symm_mem
+        self.out = symm_mem.empty((m_max, self.n), dtype=torch.bfloat16, device=device)
+        group = process_group if process_group is not None else dist.group.WORLD
+        self.handle = symm_mem.rendezvous(self.out, group=group)
+        ptrs = list(self.handle.buffer_ptrs)
+        self.peer_ptrs = [int(p) for r, p in enumerate(ptrs) if r != rank]
+
+    def forward(self, x):
+        ext = _ext()
+        m = x.shape[0]
+        assert m <= self.out.shape[0], "batch larger than the symmetric output buffer"
+        q, s = ext.per_token_quant_int8(x)
+        self.handle.barrier(channel=0)
+        ext.w8a8_gemm_allgather(q, self.w, s, self.w_scale, self.out[:m], self.rank * self.n_local, self.peer_ptrs)
+        self.handle.barrier(channel=1)
+        return self.out[:m]

@@ -118,6 +118,17 @@ DSV4_API int launch_w8a8_gemm_v5(const void* A, const void* B, const void* sa, c
 DSV4_API int launch_w8a8_gemm_ld(const void* A, const void* B, const void* sa, const void* sb, void* C,
                         int64_t ldc, int M, int N, int K, dsv4_stream_t stream);
 
+/* Fused GEMM + all-gather for a column-sharded linear layer.  The tile epilogue stores every
+ * 64-byte piece of the result to C_local and, with plain stores over NVLink, to the npeers <= 7
+ * buffers in C_peers: host array of DEVICE pointers into the other ranks' output buffers, mapped
+ * into this process (CUDA IPC / symmetric memory), each already offset to this rank's column
+ * slab; all share the row stride ldc.  N % 32 == 0.  The caller orders the ranks afterwards
+ * (a barrier) before anyone reads a full row.  No counterpart in the reference, which has no
+ * collective code. */
+DSV4_API int launch_w8a8_gemm_allgather(const void* A, const void* B, const void* sa, const void* sb,
+                               void* C_local, void* const* C_peers, int npeers, int64_t ldc, int M,
+                               int N, int K, dsv4_stream_t stream);
+
 /* Raw accumulators: C int32 [M,N] = sum_k A[m,k]*B[n,k].  The product torch._int_mm
  * supplies in w8a8_gemm_intmm_fused.hip:38-39. */
 DSV4_API int launch_w8a8_gemm_i32(const void* A, const void* B, void* C, int M, int N, int K,

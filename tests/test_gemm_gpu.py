@@ -224,3 +224,23 @@ def test_gemm_writes_into_column_slab(cabi, ext):
     cabi.w8a8_gemm_ld(A.cuda(), B.cuda(), sa.cuda(), sb.cuda(), buf3, 2048)
     assert torch.equal(buf3[:, 2048:].cpu().view(torch.int16), oracle.w8a8_gemm(A, B, sa, sb).view(torch.int16))
     assert buf3[:, :2048].abs().sum().item() == 0
+
+
+def test_gemm_fused_allgather_stores_to_every_buffer(cabi, ext):
+    # the peer buffers of the fused all-gather, emulated on one GPU: three [M, 1024] buffers, the
+    # GEMM must write the same slab into all of them and touch nothing else
+    m, n, k, width, col0 = 2048, 512, 384, 1024, 256
+    A, B, sa, sb = _operands(m, n, k, seed=9)
+    ref = oracle.w8a8_gemm(A, B, sa, sb)
+    bufs = [torch.full((m, width), 3.0, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    ext.w8a8_gemm_allgather(A.cuda(), B.cuda(), sa.cuda(), sb.cuda(), bufs[0], col0, [b.data_ptr() for b in bufs[1:]])
+    assert cabi.device_status() == 0
+    for b in bufs:
+        assert torch.equal(b[:, col0:col0 + n].cpu().view(torch.int16), ref.view(torch.int16))
+        assert (b[:, :col0] == 3.0).all() and (b[:, col0 + n:] == 3.0).all()
+    # few rows: the one-CTA-per-tile kernel takes the peer path as well
+    m2 = 100
+    bufs = [torch.zeros((m2, width), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    ext.w8a8_gemm_allgather(A[:m2].cuda(), B.cuda(), sa[:m2].cuda(), sb.cuda(), bufs[0], 0, [bufs[1].data_ptr()])
+    for b in bufs:
+        assert torch.equal(b[:, :n].cpu().view(torch.int16), ref[:m2].view(torch.int16))

@@ -1,0 +1,69 @@
+"""The two sharded configurations on real GPUs (needs at least two; skipped otherwise): one
+process per GPU over NCCL, results compared with a single-GPU run of the same seeded problem."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from bw1000_dsv4_kernels_b200 import workloads as wl
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2,
+                                 reason="needs two GPUs")]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ret):
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        from bw1000_dsv4_kernels_b200 import moe, tp_linear
+
+        # ---- column-parallel linear: NCCL all-gather and fused peer stores ----
+        m, k, n = 1024, 1024, 4096
+        inp = wl.tp_linear_inputs(rank, world, m=m, k=k, n=n, device=dev, seed=2, slab=256)
+        full = wl.tp_linear_inputs(0, 1, m=m, k=k, n=n, device=dev, seed=2, slab=256)
+        ref = tp_linear.ColumnParallelW8A8Linear(full.w, full.w_scale).forward(full.x)
+        out = tp_linear.ColumnParallelW8A8Linear(inp.w, inp.w_scale, rank, world).forward(inp.x)
+        assert torch.equal(out.contiguous().view(torch.int16), ref.view(torch.int16)), "NCCL all-gather result"
+        fused = tp_linear.FusedColumnParallelW8A8Linear(inp.w, inp.w_scale, rank, world, m_max=m, device=dev)
+        for _ in range(2):
+            out2 = fused.forward(inp.x)
+            torch.cuda.synchronize()
+            assert torch.equal(out2.view(torch.int16), ref.view(torch.int16)), "fused all-gather result"
+
+        # ---- expert-parallel MoE ----
+        t, h, e, inter, topk = 256, 1024, 16, 512, 4
+        lo, hi = moe.expert_range(rank, world, e)
+        part = wl.moe_inputs(t, h, e, inter, topk, device=dev, seed=4, expert_lo=lo, expert_hi=hi)
+        whole = wl.moe_inputs(t, h, e, inter, topk, device=dev, seed=4)
+        ref_m = moe.W8A8MoE(whole.w13, whole.w13_scale, whole.w2, whole.w2_scale, e).forward(whole.x, whole.topk_ids, whole.topk_w)
+        out_m = moe.W8A8MoE(part.w13, part.w13_scale, part.w2, part.w2_scale, e, expert_lo=lo).forward(part.x, part.topk_ids, part.topk_w)
+        err = (out_m.float() - ref_m.float()).abs().max().item()
+        assert err <= 1e-2 * ref_m.float().abs().max().item(), f"EP MoE off by {err}"
+        ret[rank] = "ok"
+    except Exception as exc:  # pragma: no cover
+        import traceback
+        ret[rank] = f"{type(exc).__name__}: {exc}\n{traceback.format_exc()[-1500:]}"
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_sharded_configurations_on_two_gpus():
+    world = 2
+    port = _free_port()
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+    assert dict(ret) == {r: "ok" for r in range(world)}, dict(ret)
