@@ -140,6 +140,26 @@ struct Scheduler {
     }
 };
 
+// One warp: prefix[e] = number of 128-row tiles of the experts before e, prefix[E] = all of them
+// (exclusive scan of ceil(segment length / 128) over the experts, into shared memory).
+__device__ __forceinline__ void build_tile_prefix(const Params& p, int* prefix, int lane) {
+    int carry = 0;
+    for (int e0 = 0; e0 < p.E; e0 += 32) {
+        const int e = e0 + lane;
+        int cnt = 0;
+        if (e < p.E) cnt = (p.offsets[e + 1] - p.offsets[e] + BM - 1) / BM;
+        int incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        if (e < p.E) prefix[e] = carry + incl - cnt;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) prefix[p.E] = carry;
+}
+
 __device__ __forceinline__ void report_wait_failure(int site) {
     atomicCAS(&g_device_status, 0, site);
 }
@@ -259,26 +279,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
         ptx::tmem_relinquish();
     }
-    if (p.offsets != nullptr) {
-        // prefix[e] = number of 128-row tiles of the experts before e (warp 2 scans)
-        if (warp == 2) {
-            int carry = 0;
-            for (int e0 = 0; e0 < p.E; e0 += 32) {
-                const int e = e0 + lane;
-                int cnt = 0;
-                if (e < p.E) cnt = (p.offsets[e + 1] - p.offsets[e] + BM - 1) / BM;
-                int incl = cnt;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int v = __shfl_up_sync(0xffffffffu, incl, o);
-                    if (lane >= o) incl += v;
-                }
-                if (e < p.E) prefix[e] = carry + incl - cnt;
-                carry += __shfl_sync(0xffffffffu, incl, 31);
-            }
-            if (lane == 0) prefix[p.E] = carry;
-        }
-    }
+    if (p.offsets != nullptr && warp == 2) build_tile_prefix(p, prefix, lane);
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
@@ -599,8 +600,8 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // and apply the channel scale once at the end of the tile.  Tile = 128 x 128.
 // ------------------------------------------------------------------------------------
 constexpr int GSN = 128;
-constexpr int kGsThreads = 320;       // producer warp, MMA warp, eight drain warps
-constexpr int kGsDrainWarps = 8;
+constexpr int kGsDrainWarps = 16;      // four per TMEM lane quarter: one hides another's tcgen05.ld latency
+constexpr int kGsThreads = 64 + 32 * kGsDrainWarps;  // producer warp, MMA warp, drain warps
 
 template <int STAGES>
 __global__ void __launch_bounds__(kGsThreads, 1)
@@ -644,23 +645,7 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
         ptx::tmem_relinquish();
     }
-    if (p.offsets != nullptr && warp == 2) {
-        int carry = 0;
-        for (int e0 = 0; e0 < p.E; e0 += 32) {
-            const int e = e0 + lane;
-            int cnt = 0;
-            if (e < p.E) cnt = (p.offsets[e + 1] - p.offsets[e] + BM - 1) / BM;
-            int incl = cnt;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int v = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += v;
-            }
-            if (e < p.E) prefix[e] = carry + incl - cnt;
-            carry += __shfl_sync(0xffffffffu, incl, 31);
-        }
-        if (lane == 0) prefix[p.E] = carry;
-    }
+    if (p.offsets != nullptr && warp == 2) build_tile_prefix(p, prefix, lane);
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
@@ -722,11 +707,14 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
         }
     } else {
-        // Eight drain warps: warps w and w+4 share TMEM lane quarter w%4 and take 64 columns each.
-        constexpr int HC = GSN / 2;
+        // Sixteen drain warps: the four warps w, w+4, w+8, w+12 share TMEM lane quarter w%4 and take
+        // 32 columns each, so each scheduler always has another drain warp to run while one waits
+        // for its tensor-memory load.
+        constexpr int HC = GSN * 4 / kGsDrainWarps;   // columns per warp
+        static_assert(HC == 32, "one 32-column tcgen05.ld per warp and K block");
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
-        float* sbs = sb_tile + quarter * GSN;  // written identically by both warps of a quarter
+        const int half = (warp - 2) >> 2;             // which 32-column group of the tile
+        float* sbs = sb_tile + quarter * GSN;         // each warp fills and reads its own 32 columns
         const bool vec_ok = c_vector_stores_ok(p);
         uint32_t blk = 0;
         bool ok = true;
@@ -771,9 +759,8 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 ptx::tc_fence_after_sync();
                 __syncwarp();  // tcgen05.ld is warp-collective
                 const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + b * GSN + half * HC;
-                uint32_t r0[32], r1[32];
-                ptx::tmem_ld_32x32b_x32(t_lane, r0);       // both loads in flight before the wait
-                ptx::tmem_ld_32x32b_x32(t_lane + 32, r1);
+                uint32_t r0[32];
+                ptx::tmem_ld_32x32b_x32(t_lane, r0);
                 ptx::tmem_ld_wait();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
@@ -785,12 +772,7 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                                            __int_as_float((int)r0[2 * j + 1] + 0x4B400000));
                     y2[j] = __ffma2_rn(__fadd2_rn(f, unbias), sg2, y2[j]);
                 }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    float2 f = make_float2(__int_as_float((int)r1[2 * j] + 0x4B400000),
-                                           __int_as_float((int)r1[2 * j + 1] + 0x4B400000));
-                    y2[16 + j] = __ffma2_rn(__fadd2_rn(f, unbias), sg2, y2[16 + j]);
-                }
+
             }
             if (!ok) break;
             if (row_ok) {
@@ -1081,6 +1063,18 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// More than 48 KB of dynamic shared memory needs an opt-in per kernel and per device; done on the
+// first launch of each kernel on each device.
+template <typename Kernel>
+bool opt_in_shared_memory(Kernel kernel, int bytes, bool (&done)[64]) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && done[dev]) return true;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+    if (dev >= 0 && dev < 64) done[dev] = true;
+    return true;
+}
+
 EncodeTiledFn encode_tiled_fn() {
     static EncodeTiledFn fn = nullptr;
     static std::once_flag once;
@@ -1131,16 +1125,9 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params&
                    cudaStream_t st) {
     using L = Smem<BN, STAGES>;
     static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
-    // the shared-memory opt-in is per device and per kernel: do it once for each
     static bool opted_in[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !opted_in[dev]) {
-        if (cudaFuncSetAttribute(gemm_i8_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 L::kDynamic) != cudaSuccess)
-            return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: cannot raise the dynamic shared memory limit");
-        if (dev >= 0 && dev < 64) opted_in[dev] = true;
-    }
+    if (!opt_in_shared_memory(gemm_i8_kernel<BN, STAGES>, L::kDynamic, opted_in))
+        return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: cannot raise the dynamic shared memory limit");
     int grid = sm_count();
     if (grid <= 0) return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: no CUDA device");
     if (max_tiles < grid) grid = max_tiles;
@@ -1155,14 +1142,8 @@ int launch_stream_variant(const CUtensorMap& tmW, const CUtensorMap& tmX, const 
     using L = StreamSmem<NTOK>;
     static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
     static bool opted_in[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !opted_in[dev]) {
-        if (cudaFuncSetAttribute(gemm_i8_stream_kernel<NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 L::kDynamic) != cudaSuccess)
-            return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: cannot raise the dynamic shared memory limit");
-        if (dev >= 0 && dev < 64) opted_in[dev] = true;
-    }
+    if (!opt_in_shared_memory(gemm_i8_stream_kernel<NTOK>, L::kDynamic, opted_in))
+        return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: cannot raise the dynamic shared memory limit");
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(n_tiles * splits), 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
@@ -1190,14 +1171,8 @@ int launch_gs_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Para
     using L = Smem<GSN, STAGES>;
     static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
     static bool opted_in[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !opted_in[dev]) {
-        if (cudaFuncSetAttribute(gemm_i8_gs_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 L::kDynamic) != cudaSuccess)
-            return fail(DSV4_ERR_LAUNCH, "grouped_gemm: cannot raise the dynamic shared memory limit");
-        if (dev >= 0 && dev < 64) opted_in[dev] = true;
-    }
+    if (!opt_in_shared_memory(gemm_i8_gs_kernel<STAGES>, L::kDynamic, opted_in))
+        return fail(DSV4_ERR_LAUNCH, "grouped_gemm: cannot raise the dynamic shared memory limit");
     int grid = sm_count();
     if (grid <= 0) return fail(DSV4_ERR_LAUNCH, "grouped_gemm: no CUDA device");
     if (max_tiles < grid) grid = max_tiles;
@@ -1211,14 +1186,8 @@ int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Pa
     using L = PairSmem<STAGES>;
     static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
     static bool opted_in[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !opted_in[dev]) {
-        if (cudaFuncSetAttribute(gemm_i8_pair_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 L::kDynamic) != cudaSuccess)
-            return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: cannot raise the dynamic shared memory limit");
-        if (dev >= 0 && dev < 64) opted_in[dev] = true;
-    }
+    if (!opt_in_shared_memory(gemm_i8_pair_kernel<STAGES>, L::kDynamic, opted_in))
+        return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: cannot raise the dynamic shared memory limit");
     const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
     int pairs = sm_count() / 2;
     if (pairs <= 0) return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: no CUDA device");
@@ -1363,6 +1332,10 @@ int read_device_status(cudaStream_t st, int* out) {
     if (v != 0) {
         const int zero = 0;
         cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+    }
+    if (v == 0) {
+        const int rc = read_row_status(&v);
+        if (rc) return rc;
     }
     if (out) *out = v;
     return 0;

@@ -51,5 +51,6 @@ int gather_rows(const void* src, const int* src_row, void* dst, int R, int row_b
 int moe_combine(const void* z, const int* dst_slot, const float* w, void* out, int T, int topk, int H,
                 int out_f32, cudaStream_t st);
 int read_device_status(cudaStream_t st, int* out);
+int read_row_status(int* out);  // status word of the row kernels (after the stream was synchronised)
 
 }  // namespace w8a8

@@ -20,6 +20,7 @@
 
 #include "w8a8_arith.cuh"
 #include "launch_common.h"
+#include "sm100_ptx.cuh"
 
 namespace w8a8 {
 
@@ -527,6 +528,121 @@ __global__ void __launch_bounds__(T, MINB) silu_mul_quant_table_kernel(
     }
 }
 
+// Persistent form used for many rows.  One CTA of 1024 threads per SM = two independent groups of
+// 512 threads that share the sigmoid table.  Each group owns a shared-memory row buffer and walks
+// its own row blocks (RPB rows of N gates + N ups each):
+//   wait (mbarrier) for the block's bulk copies -> h = silu(g)*u from shared memory into registers
+//   -> group barrier (also publishes the per-warp maxima) -> one thread starts the bulk copies of
+//   the group's NEXT block into the same buffer -> row maximum, quantise, store.
+// The copies (cp.async.bulk, one per half row, completion counted on an mbarrier) therefore overlap
+// the reduce / quantise / store part of the same group and everything the other group does, keep a
+// whole row block in flight per group without registers or load/store-unit request slots, and the
+// two groups are in different phases most of the time, so the shared-memory pipe (table gathers)
+// and the arithmetic pipes (quantisation) are busy together.
+__device__ int g_row_status = 0;  // non-zero: a bounded wait in a row kernel gave up
+
+__device__ __forceinline__ void group_barrier(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+template <int RPB, int VPT>
+__global__ void __launch_bounds__(1024, 1) silu_mul_quant_async_kernel(
+    const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
+    const int* __restrict__ mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
+    float* __restrict__ s, int M, int N, int64_t ldg, int64_t ldu) {
+    constexpr int GROUP = 512, GT = GROUP / RPB, WPG = GT / 32;  // threads per group / per row, warps per row
+    extern __shared__ uint4 smem4[];
+    __shared__ float red[2][2][RPB][WPG];  // [group][parity][row][warp]
+    __shared__ uint64_t bars[2];
+    const int V = N >> 3;
+    // [group][RPB][gate vectors V | up vectors V], then the sigmoid table
+    float* tab = reinterpret_cast<float*>(smem4 + (size_t)2 * RPB * 2 * V);
+    const int tid = threadIdx.x, grp = tid / GROUP, gtid = tid % GROUP;
+    const int gi = gtid / GT, lt = gtid % GT, lane = tid & 31, wig = lt >> 5;
+    if (valid_rows != nullptr) M = min(M, __ldg(valid_rows));
+    const int nblocks = (M + RPB - 1) / RPB;
+    const uint32_t bar = ptx::smem_u32(&bars[grp]);
+    const uint32_t half_bytes = (uint32_t)N * 2u;  // one row of gates (or ups) in bf16
+    uint4* my_buf = smem4 + (size_t)(grp * RPB) * 2 * V;
+
+    auto row_active = [&](int row) { return row < M && (mask == nullptr || mask[row] != 0); };
+    // the group's first thread: arm the barrier with the bytes to come and start the copies.  The
+    // buffer is only ever written by these copies; the kernel reads it.
+    auto issue = [&](int rb) {
+        uint32_t bytes = 0;
+        for (int r = 0; r < RPB; ++r) bytes += row_active(rb * RPB + r) ? 2u * half_bytes : 0u;
+        ptx::mbar_arrive_expect_tx(bar, bytes);
+        for (int r = 0; r < RPB; ++r) {
+            const int row = rb * RPB + r;
+            if (!row_active(row)) continue;
+            const uint32_t gdst = ptx::smem_u32(my_buf + (size_t)(r * 2) * V);
+            ptx::bulk_load(gdst, g + (int64_t)row * ldg, half_bytes, bar);
+            ptx::bulk_load(gdst + half_bytes, u + (int64_t)row * ldu, half_bytes, bar);
+        }
+    };
+
+    const int first = blockIdx.x * 2 + grp, stride = gridDim.x * 2;
+    if (gtid == 0) {
+        ptx::mbar_init(bar, 1);
+        ptx::fence_barrier_init();
+        if (first < nblocks) issue(first);
+    }
+    for (int i = tid; i < kSigTabEntries; i += 1024) tab[i] = sigmoid_table_entry(i);
+    __syncthreads();  // table complete, barriers initialised
+
+    uint32_t it = 0;
+    for (int rb = first; rb < nblocks; rb += stride, ++it) {
+        if (!ptx::mbar_wait_bounded(bar, it & 1u)) {
+            atomicCAS(&g_row_status, 0, 201);
+            break;  // every thread of the group times out on the same barrier
+        }
+        const int row = rb * RPB + gi;
+        const bool active = row_active(row);
+        const uint4* gb = my_buf + (size_t)(gi * 2) * V;
+        const uint4* ub = gb + V;
+        float2 h[VPT][4];
+        float am = 0.0f;
+        if (active) {
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int idx = lt + j * GT;
+                if (idx < V) {
+                    silu_mul8_table(gb[idx], ub[idx], tab, h[j]);
+                    am = fmaxf(am, fmaxf(fmaxf(fabsf(h[j][0].x), fabsf(h[j][0].y)), fmaxf(fabsf(h[j][1].x), fabsf(h[j][1].y))));
+                    am = fmaxf(am, fmaxf(fmaxf(fabsf(h[j][2].x), fabsf(h[j][2].y)), fmaxf(fabsf(h[j][3].x), fabsf(h[j][3].y))));
+                }
+            }
+        }
+        am = warp_max(am);
+        if (lane == 0) red[grp][it & 1u][gi][wig] = am;
+        group_barrier(1 + grp, GROUP);  // the buffer has been read by everyone; the maxima are visible
+        if (gtid == 0 && rb + stride < nblocks) issue(rb + stride);
+        float rowmax = (lane < WPG) ? red[grp][it & 1u][gi][lane] : 0.0f;
+        rowmax = warp_max(rowmax);
+        if (active) {
+            float scale, inv;
+            scale_from_amax(rowmax, scale, inv);
+            if (lt == 0) s[row] = scale;
+            const float2 inv2 = splat2(inv);
+            uint2* qr = reinterpret_cast<uint2*>(q + (int64_t)row * N);
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int idx = lt + j * GT;
+                if (idx < V) {
+                    const float2 c0 = quant_rn_lowbyte2(h[j][0], inv2);
+                    const float2 c1 = quant_rn_lowbyte2(h[j][1], inv2);
+                    const float2 c2 = quant_rn_lowbyte2(h[j][2], inv2);
+                    const float2 c3 = quant_rn_lowbyte2(h[j][3], inv2);
+                    uint2 o;
+                    o.x = pack_lowbytes(__float_as_uint(c0.x), __float_as_uint(c0.y), __float_as_uint(c1.x), __float_as_uint(c1.y));
+                    o.y = pack_lowbytes(__float_as_uint(c2.x), __float_as_uint(c2.y), __float_as_uint(c3.x), __float_as_uint(c3.y));
+                    qr[idx] = o;
+                }
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256) silu_mul_quant_generic_kernel(
     const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
     const int* __restrict__ mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
@@ -726,6 +842,41 @@ int silu_mul_quant(const void* g, const void* u, const int* mask, const int* val
         const size_t tab_smem = row_smem + kSigTabEntries * sizeof(float);
         int sms = 0;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        // rows per group pass of the persistent kernel: as many (1, 2 or 4) as keep a group's 512
+        // threads busy, while both groups' row buffers plus the table fit in shared memory
+        int rpb = V >= 512 ? 1 : V >= 256 ? 2 : 4;
+        while (rpb > 1 && (size_t)2 * rpb * row_smem + kSigTabEntries * sizeof(float) > 200 * 1024) rpb >>= 1;
+        const size_t async_smem = (size_t)2 * rpb * row_smem + kSigTabEntries * sizeof(float);
+        const int gt = 512 / rpb;
+        const int vpt = (V + gt - 1) / gt;
+        if (sms > 0 && async_smem <= 200 * 1024 && (int64_t)M >= (int64_t)4 * sms * rpb && V >= 64 && vpt <= 5) {
+            const int nblocks = (M + rpb - 1) / rpb;
+            const int grid = (nblocks + 1) / 2 < sms ? (nblocks + 1) / 2 : sms;
+#define W8A8_LAUNCH_SILU_ASYNC(R, P)                                                                         \
+    do {                                                                                                     \
+        static bool opted[64] = {};                                                                          \
+        if (dev < 0 || dev >= 64 || !opted[dev]) {                                                           \
+            cudaFuncSetAttribute(silu_mul_quant_async_kernel<R, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 200 * 1024);                                                                \
+            if (dev >= 0 && dev < 64) opted[dev] = true;                                                     \
+        }                                                                                                    \
+        silu_mul_quant_async_kernel<R, P><<<grid, 1024, async_smem, st>>>(gp, up, mask, valid_rows, qp, sp, M, N, \
+                                                                          ldg, ldu);                         \
+    } while (0)
+            switch (rpb * 8 + vpt) {
+                case 1 * 8 + 1: W8A8_LAUNCH_SILU_ASYNC(1, 1); break;
+                case 1 * 8 + 2: W8A8_LAUNCH_SILU_ASYNC(1, 2); break;
+                case 1 * 8 + 3: W8A8_LAUNCH_SILU_ASYNC(1, 3); break;
+                case 1 * 8 + 4: W8A8_LAUNCH_SILU_ASYNC(1, 4); break;
+                case 1 * 8 + 5: W8A8_LAUNCH_SILU_ASYNC(1, 5); break;
+                case 2 * 8 + 1: W8A8_LAUNCH_SILU_ASYNC(2, 1); break;
+                case 2 * 8 + 2: W8A8_LAUNCH_SILU_ASYNC(2, 2); break;
+                case 4 * 8 + 1: W8A8_LAUNCH_SILU_ASYNC(4, 1); break;
+                default: W8A8_LAUNCH_SILU_ASYNC(4, 2); break;
+            }
+#undef W8A8_LAUNCH_SILU_ASYNC
+            return check_launch("silu_mul_quant");
+        }
         if (sms > 0 && M >= 4 * sms && tab_smem <= 110 * 1024) {
             // many rows: persistent CTAs (two per SM) with the sigmoid table
             static bool tab_opted_in[64] = {};
@@ -750,6 +901,18 @@ int silu_mul_quant(const void* g, const void* u, const int* mask, const int* val
         silu_mul_quant_generic_kernel<<<grid_rows(M), 256, 0, st>>>(gp, up, mask, valid_rows, qp, sp, M, N, ldg, ldu);
     }
     return check_launch("silu_mul_quant");
+}
+
+int read_row_status(int* out) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_row_status, sizeof(int)) != cudaSuccess)
+        return fail(DSV4_ERR_LAUNCH, "device_status: cannot read the row-kernel status word");
+    if (v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_row_status, &zero, sizeof(int));
+    }
+    *out = v;
+    return 0;
 }
 
 int silu_mul(const void* g, const void* u, void* out, int M, int N, int64_t ldg, int64_t ldu,

@@ -190,18 +190,12 @@ __device__ __forceinline__ float2 silu_mul2(float2 g, float2 u) {
 }
 
 // int8 codes of two values in the low bytes of the two returned words (see quant_rn_lowbyte).
-// The product must be rounded before the add (x*inv can land exactly on a half after rounding and
-// then rounds to even; a fused multiply-add would round the unrounded product instead), so the
-// two steps are pinned as separate instructions.
+// Deliberately the scalar rounded multiply and add, not the packed f32x2 pair: the product must be
+// rounded before the add (x*inv can land exactly on a half after rounding and then rounds to even),
+// and a packed mul followed by a packed add came out of the assembler as one fused operation,
+// which rounds the unrounded product instead (1 code in 3 M differed, always on such ties).
 __device__ __forceinline__ float2 quant_rn_lowbyte2(float2 x, float2 inv2) {
-    unsigned long long xi, ii, mi, prod, sum;
-    const float2 magic = splat2(kRoundMagic);
-    xi = *reinterpret_cast<const unsigned long long*>(&x);
-    ii = *reinterpret_cast<const unsigned long long*>(&inv2);
-    mi = *reinterpret_cast<const unsigned long long*>(&magic);
-    asm volatile("mul.rn.f32x2 %0, %1, %2;" : "=l"(prod) : "l"(xi), "l"(ii));
-    asm volatile("add.rn.f32x2 %0, %1, %2;" : "=l"(sum) : "l"(prod), "l"(mi));
-    return *reinterpret_cast<float2*>(&sum);
+    return make_float2(__fadd_rn(__fmul_rn(x.x, inv2.x), kRoundMagic), __fadd_rn(__fmul_rn(x.y, inv2.y), kRoundMagic));
 }
 
 // h for the 8 gates / ups of one 16-byte vector pair.  One range test for the whole vector: if

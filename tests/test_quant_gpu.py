@@ -196,7 +196,7 @@ def test_silu_mul_masked_quant(cabi, ext):
     _eq(s2, s_ref, "scales (operator)")
 
 
-@pytest.mark.parametrize("m,n", [(640, 18432), (1500, 2048), (600, 520)])
+@pytest.mark.parametrize("m,n", [(640, 18432), (1500, 2048), (600, 520), (2400, 1024), (600, 7168)])
 def test_silu_mul_quant_many_rows_table_path(cabi, ext, m, n):
     # enough rows for the persistent kernel that looks sigmoid up in a shared-memory table; the
     # inputs include values outside the table's range (zeros, denormal-small, huge, both signs)
@@ -224,8 +224,8 @@ def test_sigmoid_table_covers_every_bf16_gate(cabi):
     g = bits[finite].to(torch.int16).view(torch.bfloat16)
     n = 1024
     rows = 640
-    pad = rows * n - g.numel()
-    g_all = torch.cat([g, g[:pad]]).view(rows, n).contiguous()
+    reps = (rows * n + g.numel() - 1) // g.numel()
+    g_all = g.repeat(reps)[:rows * n].view(rows, n).contiguous()
     u_all = torch.ones_like(g_all)
     q_ref, s_ref = oracle.silu_mul_quant(g_all, u_all)
     q, s = cabi.silu_mul_quant(g_all.cuda(), u_all.cuda())
@@ -254,3 +254,21 @@ def test_ptgq_many_elements_and_exact_multiples(cabi):
     q, s = cabi.ptgq(xm.cuda(), 128)
     _eq(s, s_ref, "scales (multiples)")
     _eq(q, q_ref, "codes (multiples)")
+
+
+def test_silu_mul_quant_many_rows_with_mask_and_row_count(cabi, ext):
+    # the persistent kernels with a row mask and with a device-side row count
+    m, n = 700, 18432
+    gu = wl.randn_bf16((m, 2 * n), seed=77)
+    mask = (torch.arange(m) % 3 != 1).to(torch.int32)
+    q_ref, s_ref = oracle.silu_mul_quant(gu[:, :n], gu[:, n:], mask)
+    gud = gu.cuda()
+    q, s = cabi.silu_mul_quant(gud[:, :n], gud[:, n:], mask.cuda())
+    _eq(q, q_ref, "codes (mask)")
+    _eq(s, s_ref, "scales (mask)")
+    valid = torch.tensor([651], dtype=torch.int32).cuda()
+    q2, s2 = ext.silu_mul_quant_rows(gud[:, :n], gud[:, n:], valid)
+    qa, sa = oracle.silu_mul_quant(gu[:651, :n], gu[:651, n:])
+    _eq(q2[:651], qa, "codes (row count)")
+    _eq(s2[:651], sa, "scales (row count)")
+    assert q2[651:].abs().sum().item() == 0 and s2[651:].abs().sum().item() == 0
