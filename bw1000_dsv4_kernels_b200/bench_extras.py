@@ -216,6 +216,21 @@ def _tp_section(ext, dev, rank, world, peaks, time_launches):
         "quant_gemm_allgather_TOPS_whole_job": round(ops / (ms_slabs * 1e-3) / 1e12, 1),
     }
     if world > 1:
+        try:
+            fused = tp_linear.FusedColumnParallelW8A8Linear(inp.w, inp.w_scale, rank, world, m_max=M, device=dev)
+            _sync(world)
+            ms_fused = _max_over_ranks(time_launches(lambda i: fused.forward(inp.x), 10, warmup=3), dev, world)
+            out["fused_quant_gemm_allgather_ms"] = round(ms_fused, 4)
+            out["fused_TOPS_whole_job"] = round(ops / (ms_fused * 1e-3) / 1e12, 1)
+            out["fused_note"] = ("one kernel: the GEMM's tile epilogue stages each bf16 tile in shared memory and sends it "
+                                 "with TMA tile stores to every rank's row-major [M,N] buffer (symmetric memory, over "
+                                 "NVLink), between two symmetric-memory barriers; includes the quantiser")
+            sent = (world - 1) * M * n_local * 2
+            out["fused_nvlink_GBps_sent_per_rank"] = round(sent / (ms_fused * 1e-3) / 1e9, 1)
+            out["fused_nvlink_frac_of_770"] = round(sent / (ms_fused * 1e-3) / 1e9 / 770.0, 4)
+            del fused
+        except Exception as exc:  # pragma: no cover
+            out["fused_error"] = f"{type(exc).__name__}: {exc}"
         recv = (world - 1) * M * n_local * 2
         ag_ms = max(ms_slabs - ms_local, 1e-6)
         out["allgather_bytes_received_per_rank"] = recv

@@ -211,7 +211,9 @@ __device__ __forceinline__ void drain_accumulator(const Params& p, uint32_t t_la
                     *reinterpret_cast<uint4*>(out + 8 * j) =
                         make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
                 // the same 64 bytes to every peer's copy of the output (plain stores over NVLink)
-                for (int d = 0; d < p.npeers; ++d) {
+#pragma unroll
+                for (int d = 0; d < 7; ++d) {
+                    if (d >= p.npeers) break;
                     __nv_bfloat16* po = static_cast<__nv_bfloat16*>(p.peerC[d]) + (int64_t)row * p.ldc + n;
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
@@ -411,13 +413,16 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 //   acc_full[a]  one in each CTA; the even CTA's commit arrives on both
 //   acc_empty[a] lives in the even CTA; the drain warps of both CTAs arrive on it
 // ------------------------------------------------------------------------------------
-template <int STAGES>
+template <int STAGES, bool TMA_STORE>
 struct PairSmem {
     static constexpr int kABytes = BM * BK;        // this CTA's 128 rows of A
     static constexpr int kBBytes = 128 * BK;       // this CTA's 128 of the tile's 256 rows of B
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTilesBytes = STAGES * kStageBytes;
-    static constexpr int kSbOff = kTilesBytes;                  // 4 warps x 256 column scales
+    // output staging for the TMA-store epilogue: 4 slabs of [128 rows][64 bf16 = 128 B], 128B-swizzled
+    static constexpr int kOutOff = kTilesBytes;
+    static constexpr int kOutBytes = TMA_STORE ? 4 * 128 * 128 : 0;
+    static constexpr int kSbOff = kOutOff + kOutBytes;          // 4 warps x 256 column scales
     static constexpr int kBarOff = kSbOff + 4 * 256 * 4;        // 8-byte aligned
     static constexpr int kNumBars = 2 * STAGES + 4;
     static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
@@ -426,11 +431,17 @@ struct PairSmem {
     static constexpr int kDynamic = kTotal + 1024;
 };
 
-template <int STAGES>
+// Tensor maps of the output slab in this rank's buffer (index 0) and in every peer's buffer.
+struct StoreMaps {
+    CUtensorMap m[8];
+    int count;
+};
+
+template <int STAGES, bool TMA_STORE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const Params p) {
-    using L = PairSmem<STAGES>;
+                    const Params p, const __grid_constant__ StoreMaps smaps) {
+    using L = PairSmem<STAGES, TMA_STORE>;
     constexpr int PBN = 256;  // tile width of the pair
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -572,9 +583,59 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             ptx::tc_fence_after_sync();
             const int row = mt * 256 + (int)rank * 128 + quarter * 32 + lane;
             const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * PBN;
-            drain_accumulator<PBN>(p, t_lane, sbs, row, row < p.M, n0, vec_ok);
-            ptx::tc_fence_before_sync();
-            __syncwarp();
+            if constexpr (!TMA_STORE) {
+                drain_accumulator<PBN>(p, t_lane, sbs, row, row < p.M, n0, vec_ok);
+            } else {
+                // Fused all-gather epilogue: the bf16 tile is staged in shared memory (four 64-column
+                // slabs, 128-byte swizzle so that the 16-byte stores of a quarter-warp hit all banks) and
+                // one thread sends it with TMA tile stores to this rank's buffer and to every peer's:
+                // full 128-byte rows per request over NVLink, no store instruction per destination.
+                const uint32_t out_base = tiles_base + L::kOutOff;
+                const int r = quarter * 32 + lane;  // row inside this CTA's 128-row half tile
+                const float sa = (row < p.M) ? __ldg(p.sa + row) : 0.0f;
+                if (warp == 2 && lane == 0) ptx::bulk_wait_group_read0();  // previous tile's stores have read the staging
+                asm volatile("bar.sync 2, %0;" ::"n"(kDrainThreads) : "memory");
+#pragma unroll 1
+                for (int cc = 0; cc < PBN / 32; ++cc) {
+                    uint32_t acc_r[32];
+                    __syncwarp();
+                    ptx::tmem_ld_32x32b_x32(t_lane + cc * 32, acc_r);
+                    ptx::tmem_ld_wait();
+                    const float4* sb4 = reinterpret_cast<const float4*>(sbs + cc * 32);
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 s4 = sb4[j];
+                        const float v0 = __fmul_rn(__fmul_rn(__int2float_rn((int)acc_r[4 * j + 0]), sa), s4.x);
+                        const float v1 = __fmul_rn(__fmul_rn(__int2float_rn((int)acc_r[4 * j + 1]), sa), s4.y);
+                        const float v2 = __fmul_rn(__fmul_rn(__int2float_rn((int)acc_r[4 * j + 2]), sa), s4.z);
+                        const float v3 = __fmul_rn(__fmul_rn(__int2float_rn((int)acc_r[4 * j + 3]), sa), s4.w);
+                        packed[2 * j] = pack_bf16x2_rn(v0, v1);
+                        packed[2 * j + 1] = pack_bf16x2_rn(v2, v3);
+                    }
+                    const uint32_t slab = out_base + (uint32_t)(cc >> 1) * (128u * 128u) + (uint32_t)r * 128u;
+                    const uint32_t chunk0 = (uint32_t)(cc & 1) * 4u;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t phys = (chunk0 + j) ^ (uint32_t)(r & 7);
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(slab + phys * 16u),
+                                     "r"(packed[4 * j]), "r"(packed[4 * j + 1]), "r"(packed[4 * j + 2]),
+                                     "r"(packed[4 * j + 3])
+                                     : "memory");
+                    }
+                }
+                ptx::fence_proxy_async_smem();  // the staged tile becomes visible to the TMA engine
+                asm volatile("bar.sync 2, %0;" ::"n"(kDrainThreads) : "memory");
+                if (warp == 2 && lane == 0) {
+                    const int y = mt * 256 + (int)rank * 128;
+                    for (int d = 0; d < smaps.count; ++d)
+#pragma unroll
+                        for (int sl = 0; sl < 4; ++sl)
+                            if (n0 + sl * 64 < p.N)
+                                ptx::tma_store_2d(&smaps.m[d], n0 + sl * 64, y, out_base + (uint32_t)sl * (128u * 128u));
+                    ptx::bulk_commit_group();
+                }
+            }
             if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
@@ -582,6 +643,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
 
     // ---------------- teardown ----------------
+    if (TMA_STORE && warp == 2 && lane == 0) ptx::bulk_wait_group0();  // this thread's tile stores are complete
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::cluster_sync();  // neither CTA leaves while the other may still touch its memory
@@ -1181,18 +1243,34 @@ int launch_gs_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Para
     return check_launch("grouped_gemm (group-scaled)");
 }
 
-template <int STAGES>
-int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, cudaStream_t st) {
-    using L = PairSmem<STAGES>;
+// bf16 [rows, cols] view with row stride ldc elements: box = 64 columns x 128 rows, 128-byte swizzle
+int make_store_map(CUtensorMap* map, void* base, uint64_t rows, uint64_t cols, uint64_t ldc) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return fail(DSV4_ERR_DRIVER, "w8a8_gemm: cuTensorMapEncodeTiled is not available");
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ldc * 2};
+    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(DSV4_ERR_DRIVER, "w8a8_gemm_allgather: cuTensorMapEncodeTiled failed for an output map");
+    return 0;
+}
+
+template <int STAGES, bool TMA_STORE>
+int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, const StoreMaps& smaps,
+                        cudaStream_t st) {
+    using L = PairSmem<STAGES, TMA_STORE>;
     static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
     static bool opted_in[64] = {};
-    if (!opt_in_shared_memory(gemm_i8_pair_kernel<STAGES>, L::kDynamic, opted_in))
+    if (!opt_in_shared_memory(gemm_i8_pair_kernel<STAGES, TMA_STORE>, L::kDynamic, opted_in))
         return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: cannot raise the dynamic shared memory limit");
     const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
     int pairs = sm_count() / 2;
     if (pairs <= 0) return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: no CUDA device");
     if (tiles < pairs) pairs = tiles;
-    gemm_i8_pair_kernel<STAGES><<<2 * pairs, kThreads, L::kDynamic, st>>>(tmA, tmB, p);
+    gemm_i8_pair_kernel<STAGES, TMA_STORE><<<2 * pairs, kThreads, L::kDynamic, st>>>(tmA, tmB, p, smaps);
     return check_launch("w8a8_gemm");
 }
 
@@ -1282,7 +1360,20 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
         if (rc2) return rc2;
         rc2 = make_tile_map(&tmB, a.B, b_rows, (uint64_t)a.K, 128);
         if (rc2) return rc2;
-        return launch_pair_variant<6>(tmA, tmB, p, st);
+        StoreMaps smaps;
+        smaps.count = 0;
+        if (a.npeers > 0) {
+            // fused all-gather: tile stores through tensor maps of this rank's slab and of every peer's
+            rc2 = make_store_map(&smaps.m[0], a.C, (uint64_t)a.M, (uint64_t)a.N, (uint64_t)p.ldc);
+            if (rc2) return rc2;
+            for (int d = 0; d < a.npeers; ++d) {
+                rc2 = make_store_map(&smaps.m[1 + d], a.peerC[d], (uint64_t)a.M, (uint64_t)a.N, (uint64_t)p.ldc);
+                if (rc2) return rc2;
+            }
+            smaps.count = 1 + a.npeers;
+            return launch_pair_variant<4, true>(tmA, tmB, p, smaps, st);
+        }
+        return launch_pair_variant<6, false>(tmA, tmB, p, smaps, st);
     }
     int rc = make_tile_map(&tmA, a.A, (uint64_t)a.M, (uint64_t)a.K, BM);
     if (rc) return rc;

@@ -70,9 +70,10 @@ class ColumnParallelW8A8Linear:
 class FusedColumnParallelW8A8Linear(ColumnParallelW8A8Linear):
     """Same layer with the exchange fused into the GEMM: the output [M, N] lives in symmetric
     memory (every rank's buffer is mapped into every other rank), and the GEMM's tile epilogue
-    stores each piece of this rank's column slab into all G buffers with plain stores over NVLink
-    (`w8a8_gemm_allgather`), so the transfer overlaps the tensor-core work tile by tile and the
-    result is row-major without a gather or a permute.  A symmetric-memory barrier on the stream
+    stages each 128 x 256 bf16 tile of this rank's column slab in shared memory and sends it with
+    TMA tile stores into all G buffers over NVLink (`w8a8_gemm_allgather`), so the transfer
+    overlaps the tensor-core work tile by tile and the result is row-major without a gather or a
+    permute.  A symmetric-memory barrier on the stream
     before the kernel keeps a rank from overwriting rows a slower peer is still reading from the
     previous call, and one after it makes every slab visible before anyone reads a full row."""
 

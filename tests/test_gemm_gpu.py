@@ -244,3 +244,18 @@ def test_gemm_fused_allgather_stores_to_every_buffer(cabi, ext):
     ext.w8a8_gemm_allgather(A[:m2].cuda(), B.cuda(), sa[:m2].cuda(), sb.cuda(), bufs[0], 0, [bufs[1].data_ptr()])
     for b in bufs:
         assert torch.equal(b[:, :n].cpu().view(torch.int16), ref[:m2].view(torch.int16))
+
+
+@pytest.mark.parametrize("m,n", [(2048, 2560), (1900, 2592)])
+def test_gemm_fused_allgather_tile_store_path(cabi, ext, m, n):
+    # enough tiles for the CTA-pair kernel, whose fused epilogue stages the tile in shared memory and
+    # sends it with TMA tile stores; ragged M, and N that is a multiple of 32 but not of 64
+    k, width, col0 = 256, 4096, 1024
+    A, B, sa, sb = _operands(m, n, k, seed=m + n)
+    ref = oracle.w8a8_gemm(A, B, sa, sb)
+    bufs = [torch.full((m, width), 5.0, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    ext.w8a8_gemm_allgather(A.cuda(), B.cuda(), sa.cuda(), sb.cuda(), bufs[0], col0, [b.data_ptr() for b in bufs[1:]])
+    assert cabi.device_status() == 0
+    for b in bufs:
+        assert torch.equal(b[:, col0:col0 + n].cpu().view(torch.int16), ref.view(torch.int16))
+        assert (b[:, :col0] == 5.0).all() and (b[:, col0 + n:] == 5.0).all()
