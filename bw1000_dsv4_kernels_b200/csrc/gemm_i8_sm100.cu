@@ -78,7 +78,7 @@ struct Smem {
     static constexpr int kSbOff = kTilesBytes;
     static constexpr int kPrefixOff = kSbOff + 4 * BN * 4;
     static constexpr int kBarOff = kPrefixOff + (kMaxExperts + 1) * 4 + 4;  // 8-byte aligned below
-    static constexpr int kNumBars = 2 * STAGES + 4;
+    static constexpr int kNumBars = 2 * STAGES + 8;  // stage full/empty + up to 4 accumulator full/empty pairs
     static constexpr int kTmemSlotOff = ((kBarOff + 7) & ~7) + kNumBars * 8;
     static constexpr int kAbortOff = kTmemSlotOff + 4;
     static constexpr int kTotal = kAbortOff + 4;
@@ -661,8 +661,9 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // fp32 registers as y = fma(float(acc_g), sa[row, g], y) while the MMAs of block g+1 run,
 // and apply the channel scale once at the end of the tile.  Tile = 128 x 128.
 // ------------------------------------------------------------------------------------
-constexpr int GSN = 128;
-constexpr int kGsDrainWarps = 16;      // four per TMEM lane quarter: one hides another's tcgen05.ld latency
+constexpr int GSN = 256;               // tile width: the wider tile halves the re-reads of the A rows from L2
+constexpr int kGsBufs = 2;             // 256-column accumulators in flight (all 512 TMEM columns)
+constexpr int kGsDrainWarps = 16;      // four per TMEM lane quarter, 64 columns each
 constexpr int kGsThreads = 64 + 32 * kGsDrainWarps;  // producer warp, MMA warp, drain warps
 
 template <int STAGES>
@@ -683,17 +684,17 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto blk_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
-    auto blk_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    auto blk_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + kGsBufs + a); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr uint32_t kTmemCols = 2 * GSN;
+    constexpr uint32_t kTmemCols = kGsBufs * GSN;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(full_bar(s), 1);
             ptx::mbar_init(empty_bar(s), 1);
         }
-        for (int a = 0; a < 2; ++a) {
+        for (int a = 0; a < kGsBufs; ++a) {
             ptx::mbar_init(blk_full_bar(a), 1);
             ptx::mbar_init(blk_empty_bar(a), kGsDrainWarps);
         }
@@ -743,12 +744,12 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             constexpr uint32_t idesc = ptx::idesc_i8(BM, GSN);
             int stage = 0;
             uint32_t phase = 0;
-            uint32_t blk = 0;  // running K-block counter: buffer = blk & 1, parity = (blk >> 1) & 1
+            uint32_t blk = 0;  // running K-block counter: buffer = blk % kGsBufs, parity = (blk / kGsBufs) & 1
             bool ok = true;
             for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
                 for (int kb = 0; kb < k_blocks; ++kb, ++blk) {
-                    const int b = blk & 1;
-                    if (!ptx::mbar_wait_bounded(blk_empty_bar(b), ((blk >> 1) & 1u) ^ 1u) ||
+                    const int b = blk % kGsBufs;
+                    if (!ptx::mbar_wait_bounded(blk_empty_bar(b), ((blk / kGsBufs) & 1u) ^ 1u) ||
                         !ptx::mbar_wait_bounded(full_bar(stage), phase) || *abort_flag) {
                         report_wait_failure(kWaitFullStage);
                         *abort_flag = 1;
@@ -769,14 +770,14 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
         }
     } else {
-        // Sixteen drain warps: the four warps w, w+4, w+8, w+12 share TMEM lane quarter w%4 and take
-        // 32 columns each, so each scheduler always has another drain warp to run while one waits
-        // for its tensor-memory load.
+        // Sixteen drain warps: warps w, w+4, w+8, w+12 share TMEM lane quarter w%4 and take 64 columns
+        // each, 16 at a time (the fp32 accumulators of the 128 x 256 tile fill half the register file,
+        // so the tensor-memory loads are kept narrow).
         constexpr int HC = GSN * 4 / kGsDrainWarps;   // columns per warp
-        static_assert(HC == 32, "one 32-column tcgen05.ld per warp and K block");
+        static_assert(HC == 64, "four 16-column tcgen05.ld per warp and K block");
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;             // which 32-column group of the tile
-        float* sbs = sb_tile + quarter * GSN;         // each warp fills and reads its own 32 columns
+        const int half = (warp - 2) >> 2;             // which 64-column quarter of the tile
+        float* sbs = sb_tile + quarter * GSN;         // each warp fills and reads its own 64 columns
         const bool vec_ok = c_vector_stores_ok(p);
         uint32_t blk = 0;
         bool ok = true;
@@ -807,12 +808,12 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             float sg_b = (row_ok && 1 < k_blocks) ? __ldg(sa_row + 1) : 0.0f;
             float sg_c = (row_ok && 2 < k_blocks) ? __ldg(sa_row + 2) : 0.0f;
             for (int kb = 0; kb < k_blocks; ++kb, ++blk) {
-                const int b = blk & 1;
+                const int b = blk % kGsBufs;
                 const float sg = sg_a;
                 sg_a = sg_b;
                 sg_b = sg_c;
                 sg_c = (row_ok && kb + 3 < k_blocks) ? __ldg(sa_row + kb + 3) : 0.0f;
-                if (!ptx::mbar_wait_bounded(blk_full_bar(b), (blk >> 1) & 1u) || *abort_flag) {
+                if (!ptx::mbar_wait_bounded(blk_full_bar(b), (blk / kGsBufs) & 1u) || *abort_flag) {
                     report_wait_failure(kWaitAccFull);
                     *abort_flag = 1;
                     ok = false;
@@ -821,20 +822,25 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 ptx::tc_fence_after_sync();
                 __syncwarp();  // tcgen05.ld is warp-collective
                 const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + b * GSN + half * HC;
-                uint32_t r0[32];
-                ptx::tmem_ld_32x32b_x32(t_lane, r0);
-                ptx::tmem_ld_wait();
-                ptx::tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(blk_empty_bar(b));  // registers hold the block now
                 const float2 sg2 = splat2(sg), unbias = splat2(-12582912.0f);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    float2 f = make_float2(__int_as_float((int)r0[2 * j] + 0x4B400000),
-                                           __int_as_float((int)r0[2 * j + 1] + 0x4B400000));
-                    y2[j] = __ffma2_rn(__fadd2_rn(f, unbias), sg2, y2[j]);
+                for (int cc = 0; cc < HC / 16; ++cc) {
+                    uint32_t r0[16];
+                    ptx::tmem_ld_32x32b_x16(t_lane + cc * 16, r0);
+                    ptx::tmem_ld_wait();
+                    if (cc == HC / 16 - 1) {
+                        // the last columns are in registers: the accumulator can be overwritten
+                        ptx::tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(blk_empty_bar(b));
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float2 f = make_float2(__int_as_float((int)r0[2 * j] + 0x4B400000),
+                                               __int_as_float((int)r0[2 * j + 1] + 0x4B400000));
+                        y2[cc * 8 + j] = __ffma2_rn(__fadd2_rn(f, unbias), sg2, y2[cc * 8 + j]);
+                    }
                 }
-
             }
             if (!ok) break;
             if (row_ok) {
@@ -1331,7 +1337,7 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
         if (rc3) return rc3;
         rc3 = make_tile_map(&tmB, a.B, b_rows, (uint64_t)a.K, GSN);
         if (rc3) return rc3;
-        return launch_gs_variant<6>(tmA, tmB, p, tiles_m_bound * ((a.N + GSN - 1) / GSN), st);
+        return launch_gs_variant<4>(tmA, tmB, p, tiles_m_bound * ((a.N + GSN - 1) / GSN), st);
     }
     // Few tokens: stream the weight once, tokens on the MMA's N axis, K split over a cluster
     if (!grouped && a.M <= 256 && a.npeers == 0) {
