@@ -453,16 +453,21 @@ def run_ours(args):
                       f"step i+1 runs on a second stream beside the GEMM of step i (independent batches)",
         },
         "roofline": {
-            "kernel": "gemm_i8_kernel<256,4> (tcgen05 kind::i8)", "bound": "tensor", "achieved": gemm_tops,
+            "kernel": "gemm_i8_pair_kernel (tcgen05.mma.cta_group::2.kind::i8, 256x256 tile per CTA pair)", "bound": "tensor", "achieved": gemm_tops,
             "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tops / int8_peak,
             "peak_source": f"2 x cuBLAS bf16 burst ({peaks['bf16_tflops']} TF/s, {peaks['source']}); int8 ops; "
                            f"nominal dense int8 4500",
-            "traffic": None, "launch_us": ms_gemm * 1e3,
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this shape, from an
+            # ncu capture (A and B are read exactly once; most of C is still in L2 when the kernel ends)
+            "traffic": 44100608 + 1224192, "algorithmic_bytes": gemm_bytes(M_ROWS, N_DIM, K_DIM),
+            "launch_us": ms_gemm * 1e3,
         },
         "kernels": {
             "add_rmsnorm_quant": {"bound": "hbm", "achieved": quant_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                   "frac": quant_gbs / peaks["hbm_gbs"], "launch_us": ms_quant * 1e3,
-                                  "bytes": quant_bytes_add_rmsnorm(M_ROWS, K_DIM)},
+                                  "bytes": quant_bytes_add_rmsnorm(M_ROWS, K_DIM),
+                                  # from an ncu capture of this launch (the writes are still in L2)
+                                  "traffic": 58749696 + 1737728},
         },
         "serial": {"ms_per_step": ms_serial, "value": ops_step * world / (ms_serial * 1e-3) / 1e12, "unit": "TOPS",
                    "note": "the same chain with every kernel on one stream (no overlap between steps), rank 0's time"},

@@ -176,10 +176,10 @@ __global__ void __launch_bounds__(256) ptgq_vec_kernel(const uint4* __restrict__
                 float e[8];
                 unpack8(v[u], e);
                 uint2 o2;
-                o2.x = pack_i8x4(quant_trunc_div_rcp(e[0], scale, rcp), quant_trunc_div_rcp(e[1], scale, rcp),
-                                 quant_trunc_div_rcp(e[2], scale, rcp), quant_trunc_div_rcp(e[3], scale, rcp));
-                o2.y = pack_i8x4(quant_trunc_div_rcp(e[4], scale, rcp), quant_trunc_div_rcp(e[5], scale, rcp),
-                                 quant_trunc_div_rcp(e[6], scale, rcp), quant_trunc_div_rcp(e[7], scale, rcp));
+                o2.x = pack_lowbytes(quant_trunc_div_rcp(e[0], scale, rcp), quant_trunc_div_rcp(e[1], scale, rcp),
+                                     quant_trunc_div_rcp(e[2], scale, rcp), quant_trunc_div_rcp(e[3], scale, rcp));
+                o2.y = pack_lowbytes(quant_trunc_div_rcp(e[4], scale, rcp), quant_trunc_div_rcp(e[5], scale, rcp),
+                                     quant_trunc_div_rcp(e[6], scale, rcp), quant_trunc_div_rcp(e[7], scale, rcp));
                 q[f] = o2;
             }
         }
@@ -844,8 +844,12 @@ int silu_mul_quant(const void* g, const void* u, const int* mask, const int* val
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         // rows per group pass of the persistent kernel: as many (1, 2 or 4) as keep a group's 512
         // threads busy, while both groups' row buffers plus the table fit in shared memory
-        int rpb = V >= 512 ? 1 : V >= 256 ? 2 : 4;
-        while (rpb > 1 && (size_t)2 * rpb * row_smem + kSigTabEntries * sizeof(float) > 200 * 1024) rpb >>= 1;
+        // about 64 KB of row data per group pass (so that enough bytes are in flight), at most 8 rows
+        int rpb = 1;
+        while (rpb < 8 && (size_t)(2 * rpb) * row_smem <= 64 * 1024) rpb <<= 1;
+        while (rpb > 1 && ((size_t)2 * rpb * row_smem + kSigTabEntries * sizeof(float) > 200 * 1024 ||
+                           (V + 512 / rpb - 1) / (512 / rpb) > 5))
+            rpb >>= 1;
         const size_t async_smem = (size_t)2 * rpb * row_smem + kSigTabEntries * sizeof(float);
         const int gt = 512 / rpb;
         const int vpt = (V + gt - 1) / gt;
@@ -853,7 +857,7 @@ int silu_mul_quant(const void* g, const void* u, const int* mask, const int* val
             const int nblocks = (M + rpb - 1) / rpb;
             const int grid = (nblocks + 1) / 2 < sms ? (nblocks + 1) / 2 : sms;
 #define W8A8_LAUNCH_SILU_ASYNC(R, P)                                                                         \
-    do {                                                                                                     \
+    case R * 8 + P: {                                                                                        \
         static bool opted[64] = {};                                                                          \
         if (dev < 0 || dev >= 64 || !opted[dev]) {                                                           \
             cudaFuncSetAttribute(silu_mul_quant_async_kernel<R, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
@@ -862,18 +866,18 @@ int silu_mul_quant(const void* g, const void* u, const int* mask, const int* val
         }                                                                                                    \
         silu_mul_quant_async_kernel<R, P><<<grid, 1024, async_smem, st>>>(gp, up, mask, valid_rows, qp, sp, M, N, \
                                                                           ldg, ldu);                         \
-    } while (0)
+    } break
+#define W8A8_LAUNCH_SILU_ASYNC_ROWS(R)                                                                       \
+    W8A8_LAUNCH_SILU_ASYNC(R, 1); W8A8_LAUNCH_SILU_ASYNC(R, 2); W8A8_LAUNCH_SILU_ASYNC(R, 3);                  \
+    W8A8_LAUNCH_SILU_ASYNC(R, 4); W8A8_LAUNCH_SILU_ASYNC(R, 5)
             switch (rpb * 8 + vpt) {
-                case 1 * 8 + 1: W8A8_LAUNCH_SILU_ASYNC(1, 1); break;
-                case 1 * 8 + 2: W8A8_LAUNCH_SILU_ASYNC(1, 2); break;
-                case 1 * 8 + 3: W8A8_LAUNCH_SILU_ASYNC(1, 3); break;
-                case 1 * 8 + 4: W8A8_LAUNCH_SILU_ASYNC(1, 4); break;
-                case 1 * 8 + 5: W8A8_LAUNCH_SILU_ASYNC(1, 5); break;
-                case 2 * 8 + 1: W8A8_LAUNCH_SILU_ASYNC(2, 1); break;
-                case 2 * 8 + 2: W8A8_LAUNCH_SILU_ASYNC(2, 2); break;
-                case 4 * 8 + 1: W8A8_LAUNCH_SILU_ASYNC(4, 1); break;
-                default: W8A8_LAUNCH_SILU_ASYNC(4, 2); break;
+                W8A8_LAUNCH_SILU_ASYNC_ROWS(1);
+                W8A8_LAUNCH_SILU_ASYNC_ROWS(2);
+                W8A8_LAUNCH_SILU_ASYNC_ROWS(4);
+                W8A8_LAUNCH_SILU_ASYNC_ROWS(8);
+                default: return fail(DSV4_ERR_LAUNCH, "silu_mul_quant: no kernel variant for this row length");
             }
+#undef W8A8_LAUNCH_SILU_ASYNC_ROWS
 #undef W8A8_LAUNCH_SILU_ASYNC
             return check_launch("silu_mul_quant");
         }

@@ -77,11 +77,14 @@ __device__ __forceinline__ int quant_trunc_div(float x, float scale) {
 // q1 = fma(r, rcp, q0) is the correctly rounded x/scale for operands in the normal range
 // (the final step of the standard division algorithm); below 1 in magnitude the truncation is
 // zero whatever the last bit.  Checked against true division in the GPU tests.
-__device__ __forceinline__ int quant_trunc_div_rcp(float x, float scale, float rcp) {
+// Returns the code in the low byte of the result (two's complement).  No clamp: for a finite group
+// |x| <= amax and scale = RN(amax/127), so |x/scale| <= 127*(1+2^-23) and the truncation is within
+// [-127, 127]; groups containing Inf or NaN give unspecified codes.
+__device__ __forceinline__ uint32_t quant_trunc_div_rcp(float x, float scale, float rcp) {
     const float q0 = __fmul_rn(x, rcp);
     const float r = __fmaf_rn(-q0, scale, x);
     const float q1 = __fmaf_rn(r, rcp, q0);
-    return max(-128, min(127, __float2int_rz(q1)));
+    return (uint32_t)__float2int_rz(q1);
 }
 
 __device__ __forceinline__ uint32_t pack_i8x4(int a, int b, int c, int d) {
