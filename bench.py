@@ -190,12 +190,20 @@ def calibrate_oracle_rows(target_s: float) -> int:
 
 
 def cpu_baseline_leg(target_s: float = 12.0):
-    rows = calibrate_oracle_rows(target_s)
-    dt = oracle_chain_rate(rows)
+    """The oracle on a bounded sample: as many rows as fit about target_s / 4 seconds, repeated until
+    about target_s seconds of CPU work have been spent; the best pass is reported."""
+    rows = calibrate_oracle_rows(target_s / 4.0)
+    best, spent, passes = None, 0.0, 0
+    while passes < 2 or (spent < target_s and passes < 8):
+        dt = oracle_chain_rate(rows)
+        best = dt if best is None else min(best, dt)
+        spent += dt
+        passes += 1
     ops = 2.0 * rows * N_DIM * K_DIM
-    return {"value": ops / dt / 1e12, "unit": "TOPS", "cores": os.cpu_count(), "kind": "port",
+    return {"value": ops / best / 1e12, "unit": "TOPS", "cores": os.cpu_count(), "kind": "port",
             "sample": f"{rows} of {M_ROWS} rows of the same workload (add_rmsnorm_quant -> w8a8_gemm, "
-                      f"K={K_DIM}, N={N_DIM}), C oracle with OpenMP on all host threads, {dt:.2f} s"}
+                      f"K={K_DIM}, N={N_DIM}), C oracle with OpenMP on all host threads, best of {passes} passes "
+                      f"({best:.2f} s; {spent:.1f} s of CPU work in total)"}
 
 
 def run_reference_arm(args):
