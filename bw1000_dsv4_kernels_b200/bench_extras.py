@@ -179,7 +179,9 @@ def _moe_section(ext, dev, rank, world, peaks, time_launches):
     tr = layer.last_trace
     q, sg = ext.per_token_group_quant_int8(inp.x, 128)
     valid = tr.offsets[hi - lo:]
+    logits = torch.randn((T, E), device=dev, generator=torch.Generator(device=dev).manual_seed(0))
     stages = {
+        "moe_topk": lambda i: ext.moe_topk(logits, topk),
         "per_token_group_quant_int8": lambda i: ext.per_token_group_quant_int8(inp.x, 128),
         "moe_segments": lambda i: ext.moe_segments(inp.topk_ids, hi - lo, lo),
         "gather_rows": lambda i: ext.gather_rows(q, tr.src_row, sg, valid),

@@ -178,6 +178,10 @@ int launch_gather_rows(const void* src, const int* src_row, void* dst, int R, in
     return gather_rows(src, src_row, dst, R, row_bytes, src_scale, dst_scale, scales_per_row, valid_rows, cs(stream));
 }
 
+int launch_moe_topk(const float* logits, int T, int E, int k, int* topk_ids, float* topk_w, dsv4_stream_t stream) {
+    return moe_topk(logits, T, E, k, topk_ids, topk_w, cs(stream));
+}
+
 int launch_moe_combine(const void* z, const int* dst_slot, const float* topk_w, void* out, int T, int topk, int H,
                        int out_f32, dsv4_stream_t stream) {
     return moe_combine(z, dst_slot, topk_w, out, T, topk, H, out_f32, cs(stream));

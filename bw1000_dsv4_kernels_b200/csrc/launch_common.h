@@ -48,6 +48,7 @@ int moe_segments(const int* topk_ids, int T, int topk, int E, int expert_lo, int
 int gather_rows(const void* src, const int* src_row, void* dst, int R, int row_bytes,
                 const float* src_scale, float* dst_scale, int scales_per_row, const int* valid_rows,
                 cudaStream_t st);
+int moe_topk(const float* logits, int T, int E, int k, int* ids, float* weights, cudaStream_t st);
 int moe_combine(const void* z, const int* dst_slot, const float* w, void* out, int T, int topk, int H,
                 int out_f32, cudaStream_t st);
 int read_device_status(cudaStream_t st, int* out);

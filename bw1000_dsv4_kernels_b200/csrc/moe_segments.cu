@@ -254,7 +254,65 @@ __global__ void __launch_bounds__(128) moe_combine_kernel(const __nv_bfloat16* _
     }
 }
 
+// Router top-k: one warp per token.  Lane l holds logits l, l+32, ...; k rounds of a warp-wide
+// arg-max (larger value wins, ties go to the lower expert index) pick the experts in descending
+// order; the weights are the softmax over the k selected logits (exp computed in fp32 with the
+// selected maximum subtracted, the engine's "renormalised top-k softmax").
+template <int MAX_PER_LANE>
+__global__ void __launch_bounds__(256) moe_topk_kernel(const float* __restrict__ logits, int T, int E, int k,
+                                                       int* __restrict__ ids, float* __restrict__ weights) {
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < T; t += warps) {
+        const float* row = logits + (int64_t)t * E;
+        float v[MAX_PER_LANE];
+#pragma unroll
+        for (int j = 0; j < MAX_PER_LANE; ++j) {
+            const int e = lane + 32 * j;
+            v[j] = (e < E) ? __ldg(row + e) : -INFINITY;
+        }
+        float first = 0.0f, denom = 0.0f, mine = 0.0f;
+        for (int r = 0; r < k; ++r) {
+            float best = -INFINITY;
+            int best_e = 0x7fffffff;
+#pragma unroll
+            for (int j = 0; j < MAX_PER_LANE; ++j) {
+                const int e = lane + 32 * j;
+                if (v[j] > best) { best = v[j]; best_e = e; }   // ascending e: the first maximum of the lane
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+                if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+            }
+            if (r == 0) first = best;
+            const float w = expf(best - first);
+            denom += w;
+            if (lane == r) mine = w;            // lane r keeps the r-th weight (k <= 32)
+            if (lane == 0) ids[(int64_t)t * k + r] = best_e;
+#pragma unroll
+            for (int j = 0; j < MAX_PER_LANE; ++j)
+                if (lane + 32 * j == best_e) v[j] = -INFINITY;
+        }
+        if (lane < k) weights[(int64_t)t * k + lane] = mine / denom;
+    }
+}
+
 }  // namespace
+
+int moe_topk(const float* logits, int T, int E, int k, int* ids, float* weights, cudaStream_t st) {
+    if (T == 0) return 0;
+    if (T < 0 || E <= 0 || k <= 0 || k > 32 || k > E || E > 1024)
+        return fail(DSV4_ERR_ARG, "moe_topk: need 1 <= k <= min(32, E) and E <= 1024");
+    if (logits == nullptr || ids == nullptr || weights == nullptr) return fail(DSV4_ERR_ARG, "moe_topk: null pointer");
+    const int blocks = (T + 7) / 8;
+    if (E <= 256)
+        moe_topk_kernel<8><<<blocks, 256, 0, st>>>(logits, T, E, k, ids, weights);
+    else
+        moe_topk_kernel<32><<<blocks, 256, 0, st>>>(logits, T, E, k, ids, weights);
+    return check_launch("moe_topk");
+}
 
 int moe_combine(const void* z, const int* dst_slot, const float* w, void* out, int T, int topk, int H, int out_f32,
                 cudaStream_t st) {

@@ -333,6 +333,20 @@ std::vector<Tensor> gather_rows_stream(Tensor src, Tensor src_row, c10::optional
     return {dst};
 }
 
+// router top-k: logits fp32 [T,E] -> [ids int32 [T,k], weights fp32 [T,k]]
+std::vector<Tensor> moe_topk_stream(Tensor logits, int64_t k, int64_t stream_ptr) {
+    check_cuda(logits, "logits", torch::kFloat32);
+    TORCH_CHECK(logits.dim() == 2 && logits.is_contiguous(), "logits must be a contiguous [T,E] tensor");
+    c10::cuda::CUDAGuard guard(logits.device());
+    const int T = to_int(logits.size(0), "T"), E = to_int(logits.size(1), "E");
+    auto ids = torch::empty({T, k}, logits.options().dtype(torch::kInt32));
+    auto w = torch::empty({T, k}, logits.options());
+    check_status(launch_moe_topk(static_cast<const float*>(logits.data_ptr()), T, E, to_int(k, "k"),
+                                 static_cast<int*>(ids.data_ptr()), static_cast<float*>(w.data_ptr()),
+                                 as_stream(stream_ptr)));
+    return {ids, w};
+}
+
 // out[t] = sum_j w[t,j] * z[dst_slot[t,j]]  (bf16, or fp32 partial sums when out_f32)
 Tensor moe_combine_stream(Tensor z, Tensor dst_slot, Tensor topk_w, bool out_f32, int64_t stream_ptr) {
     check_cuda(z, "z", torch::kBFloat16);
@@ -447,6 +461,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         return silu_mul_quant_rows_stream(g, u, valid, current_stream_ptr());
     });
     m.def("silu_mul_quant_rows_stream", &silu_mul_quant_rows_stream);
+    m.def("moe_topk", [](Tensor logits, int64_t k) { return moe_topk_stream(logits, k, current_stream_ptr()); });
+    m.def("moe_topk_stream", &moe_topk_stream);
     m.def("moe_combine", [](Tensor z, Tensor slot, Tensor w, bool f32) {
         return moe_combine_stream(z, slot, w, f32, current_stream_ptr());
     }, py::arg("z"), py::arg("dst_slot"), py::arg("topk_w"), py::arg("out_f32") = false);

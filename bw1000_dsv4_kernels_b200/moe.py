@@ -2,6 +2,7 @@
 around its grouped GEMM (DSV4_OPERATOR_ANALYSIS.md:38-48) -- quantise, gate/up grouped GEMM,
 silu_mul_quant, down grouped GEMM, weighted sum -- with expert parallelism across ranks.
 
+    routing          : moe_topk(router_logits, k)                     ids int32 [T,k], weights fp32 [T,k]
     group quantiser  : per_token_group_quant_int8(x, 128)            [T,H] -> int8, fp32 [T,H/128]
     segments         : moe_segments(topk_ids, E_local, expert_lo)     expert offsets on the device
     permute          : gather_rows(q, src_row, scales)                rows in expert order
@@ -95,6 +96,13 @@ class W8A8MoE:
         if self.pg is not None or dist.is_initialized():
             dist.all_reduce(part, group=self.pg)
         return part.to(torch.bfloat16)
+
+
+def route(router_logits: torch.Tensor, topk: int):
+    """Router top-k on the device: fp32 logits [T,E] -> (ids int32 [T,topk], weights fp32 [T,topk] =
+    softmax over the selected logits).  Ties go to the lower expert index."""
+    ids, w = _ext().moe_topk(router_logits, topk)
+    return ids, w
 
 
 def expert_range(rank: int, world: int, num_experts: int):

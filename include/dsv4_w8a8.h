@@ -154,6 +154,12 @@ DSV4_API int launch_grouped_gemm(const void* A, const void* W, const void* sa, c
                         const int* expert_offsets, void* C, int R, int E, int N, int K,
                         int sa_groups, dsv4_stream_t stream);
 
+/* Router top-k.  logits fp32 [T,E] (E <= 1024) -> topk_ids int32 [T,k] in descending order of logit
+ * (ties: lower expert index first), topk_w fp32 [T,k] = softmax over the k selected logits.
+ * The engine's routing step (DSV4_OPERATOR_ANALYSIS.md:40); the reference has no kernel for it. */
+DSV4_API int launch_moe_topk(const float* logits, int T, int E, int k, int* topk_ids, float* topk_w,
+                    dsv4_stream_t stream);
+
 /* Segment offsets and the token permutation from top-k routing ids.
  * topk_ids int32 [T, topk] -> expert_offsets int32 [E+1] for the E experts
  * [expert_lo, expert_lo + E) (expert_lo = 0 and E = all experts on one GPU; a slice under

@@ -173,5 +173,15 @@ def moe_combine(z: torch.Tensor, dst_slot: torch.Tensor, topk_w: torch.Tensor, o
     return out
 
 
+def moe_topk(logits: torch.Tensor, k: int):
+    """-> (ids int32 [T,k] descending, ties to the lower index; weights fp32 [T,k] softmax over the selection)."""
+    logits = logits.contiguous().float()
+    t, e = logits.shape
+    ids = torch.empty((t, k), dtype=torch.int32)
+    w = torch.empty((t, k), dtype=torch.float32)
+    lib().oracle_moe_topk(_p(logits), ctypes.c_int(t), ctypes.c_int(e), ctypes.c_int(k), _p(ids), _p(w))
+    return ids, w
+
+
 def exp_fixed(x: float) -> float:
     return float(lib().oracle_exp(ctypes.c_float(x)))

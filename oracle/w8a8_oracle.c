@@ -398,3 +398,28 @@ void oracle_moe_combine(const uint16_t* z, const int32_t* dst_slot, const float*
             if (out_bf16) out_bf16[(int64_t)t * H + h] = f32_to_bf16(acc);
         }
 }
+
+/* Router top-k (the engine's routing step, DSV4_OPERATOR_ANALYSIS.md:40): k rounds of arg-max,
+ * larger logit first, ties to the lower expert index; weights = softmax over the selected logits
+ * with the first (largest) one subtracted, exp in fp32 (expf), sum in selection order. */
+void oracle_moe_topk(const float* logits, int T, int E, int k, int32_t* ids, float* w) {
+#pragma omp parallel for schedule(static)
+    for (int t = 0; t < T; ++t) {
+        const float* row = logits + (int64_t)t * E;
+        char* taken = (char*)calloc((size_t)E, 1);
+        float first = 0.0f, denom = 0.0f;
+        for (int r = 0; r < k; ++r) {
+            int best = -1;
+            for (int e = 0; e < E; ++e)
+                if (!taken[e] && (best < 0 || row[e] > row[best])) best = e;
+            taken[best] = 1;
+            ids[(int64_t)t * k + r] = best;
+            if (r == 0) first = row[best];
+            const float x = expf(row[best] - first);
+            w[(int64_t)t * k + r] = x;
+            denom += x;
+        }
+        for (int r = 0; r < k; ++r) w[(int64_t)t * k + r] = w[(int64_t)t * k + r] / denom;
+        free(taken);
+    }
+}

@@ -132,6 +132,14 @@ def moe_segments(ids, num_experts, expert_lo=0):
     return off, src, dst
 
 
+def moe_topk(logits, k):
+    t, e = logits.shape
+    ids = torch.empty((t, k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((t, k), dtype=torch.float32, device=logits.device)
+    _check(lib().launch_moe_topk(_p(logits), t, e, k, _p(ids), _p(w), _stream()))
+    return ids, w
+
+
 def moe_combine(z, dst_slot, topk_w, out_f32=False):
     t, topk = topk_w.shape
     out = torch.empty((t, z.shape[1]), dtype=torch.float32 if out_f32 else torch.bfloat16, device=z.device)

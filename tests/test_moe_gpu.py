@@ -136,3 +136,20 @@ def test_moe_expert_slice_partials_sum_to_full():
         total += part
     err = (total.cpu() - ref.float()).abs().max().item()
     assert err <= 1e-2 * ref.float().abs().max().item()
+
+
+@pytest.mark.parametrize("t,e,k", [(4096, 256, 8), (33, 64, 6), (7, 384, 8), (5, 8, 8), (1, 256, 1)])
+def test_moe_topk_matches_oracle(cabi, ext, t, e, k):
+    logits = torch.randn((t, e), generator=torch.Generator().manual_seed(t + e))
+    logits[0, : min(e, 5)] = 1.25              # ties: the lower expert index wins
+    ids_ref, w_ref = oracle.moe_topk(logits, k)
+    ids, w = cabi.moe_topk(logits.cuda(), k)
+    assert torch.equal(ids.cpu(), ids_ref)
+    # device expf and libm expf may differ in the last bit
+    assert torch.allclose(w.cpu(), w_ref, rtol=2e-6, atol=1e-9)
+    ids2, w2 = ext.moe_topk(logits.cuda(), k)
+    assert torch.equal(ids2.cpu(), ids_ref) and torch.allclose(w2.cpu(), w_ref, rtol=2e-6, atol=1e-9)
+    # same set (and order) as torch.topk where there are no ties
+    tv, ti = torch.topk(logits[1:], k, dim=-1)
+    assert torch.equal(ids_ref[1:].long(), ti)
+    assert torch.allclose(w_ref[1:], torch.softmax(tv, dim=-1), rtol=1e-5, atol=1e-8)
