@@ -13,15 +13,15 @@ OUT_DIR = os.path.join(HERE, "_build")
 OUT = os.path.join(OUT_DIR, "libw8a8_oracle.so")
 
 
-def _cpu_has_fma() -> bool:
+def _cpu_flags() -> set:
     try:
         with open("/proc/cpuinfo") as f:
             for line in f:
                 if line.startswith("flags"):
-                    return " fma " in line + " "
+                    return set(line.split(":", 1)[1].split())
     except OSError:
         pass
-    return False
+    return set()
 
 
 def build(force: bool = False) -> str:
@@ -31,11 +31,16 @@ def build(force: bool = False) -> str:
             and os.path.getmtime(OUT) >= os.path.getmtime(__file__)):
         return OUT
     os.makedirs(OUT_DIR, exist_ok=True)
-    cmd = ["gcc", "-O2", "-fopenmp", "-ffp-contract=off", "-fno-fast-math", "-fPIC", "-shared",
+    # -O3 vectorises the int8 dot products; floating-point results do not depend on the level
+    # (no fast-math, no contraction)
+    cmd = ["gcc", "-O3", "-fopenmp", "-ffp-contract=off", "-fno-fast-math", "-fPIC", "-shared",
            "-std=c11", "-Wall", "-o", OUT, SRC, "-lm"]
-    if _cpu_has_fma():
+    flags = _cpu_flags()
+    if "fma" in flags:
         # fmaf() then compiles to one instruction; the value is the same either way
         cmd.insert(1, "-mfma")
+    if "avx2" in flags:
+        cmd.insert(1, "-mavx2")
     subprocess.run(cmd, check=True)
     return OUT
 

@@ -22,6 +22,11 @@ def lib() -> ctypes.CDLL:
     return L
 
 
+def set_num_threads(n: int) -> int:
+    """OpenMP threads the oracle uses (0 = leave unchanged); returns the count in effect."""
+    return int(lib().oracle_set_num_threads(ctypes.c_int(n)))
+
+
 def _p(t: torch.Tensor) -> ctypes.c_void_p:
     assert t.device.type == "cpu" and t.is_contiguous(), "oracle takes contiguous CPU tensors"
     return ctypes.c_void_p(t.data_ptr())

@@ -22,9 +22,17 @@
  * bf16 values travel as uint16_t bit patterns.
  */
 #include <math.h>
+#include <omp.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+
+/* Number of OpenMP threads for the loops below (launchers often export OMP_NUM_THREADS=1);
+ * n <= 0 leaves the current setting.  Returns the thread count now in effect. */
+int oracle_set_num_threads(int n) {
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+}
 
 /* ---- bf16 ------------------------------------------------------------------------- */
 static inline float bf16_to_f32(uint16_t h) {
