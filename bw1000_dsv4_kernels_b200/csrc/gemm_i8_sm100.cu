@@ -939,6 +939,14 @@ gemm_i8_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     const int n0 = nt * 128;
     constexpr uint32_t kTmemCols = NTOK < 32 ? 32 : NTOK;
 
+    // this CTA's share of the K blocks
+    const int k_blocks = (p.K + BK - 1) / BK;
+    const int kb0 = (int)((int64_t)k_blocks * split / S), kb1 = (int)((int64_t)k_blocks * (split + 1) / S);
+    // the first ring-full of loads needs no wait on an empty stage: it is issued before the block-wide
+    // set-up barrier, so the weight stream starts while tensor memory is still being allocated
+    const int prologue = (kb1 - kb0) < STAGES ? (kb1 - kb0) : STAGES;
+    bool ok = true;
+
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(full_bar(s), 1);
@@ -948,8 +956,12 @@ gemm_i8_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async_smem();
-        ptx::prefetch_tensormap(&tmW);
-        ptx::prefetch_tensormap(&tmX);
+        for (int i = 0; i < prologue; ++i) {
+            const uint32_t w_dst = tiles_base + i * L::kStageBytes;
+            ptx::mbar_arrive_expect_tx(full_bar(i), L::kStageBytes);
+            ptx::tma_load_2d(w_dst, &tmW, (kb0 + i) * BK, n0, full_bar(i));
+            ptx::tma_load_2d(w_dst + L::kWBytes, &tmX, (kb0 + i) * BK, 0, full_bar(i));
+        }
     }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
@@ -960,16 +972,11 @@ gemm_i8_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    // this CTA's share of the K blocks
-    const int k_blocks = (p.K + BK - 1) / BK;
-    const int kb0 = (int)((int64_t)k_blocks * split / S), kb1 = (int)((int64_t)k_blocks * (split + 1) / S);
-    bool ok = true;
-
     if (warp == 0) {
         if (ptx::elect_one()) {
-            int stage = 0;
-            uint32_t phase = 0;
-            for (int kb = kb0; kb < kb1; ++kb) {
+            int stage = prologue == STAGES ? 0 : prologue;
+            uint32_t phase = prologue == STAGES ? 1u : 0u;
+            for (int kb = kb0 + prologue; kb < kb1; ++kb) {
                 if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u) || *abort_flag) {
                     report_wait_failure(kWaitEmptyStage);
                     *abort_flag = 1;
