@@ -170,16 +170,19 @@ __global__ void __launch_bounds__(256) ptgq_vec_kernel(const uint4* __restrict__
 #pragma unroll
             for (int o = LPG / 2; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
             if (f < nvec) {
-                const float scale = __fdiv_rn(fmaxf(am, kAmaxFloor), 127.0f);
+                const float scale = div127_rn(fmaxf(am, kAmaxFloor));
                 const float rcp = __frcp_rn(scale);
                 if ((threadIdx.x & (LPG - 1)) == 0) s[f / LPG] = scale;
-                float e[8];
-                unpack8(v[u], e);
+                const float2 rcp2 = make_float2(rcp, rcp), nscale2 = make_float2(-scale, -scale);
+                const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+                uint32_t c[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    quant_trunc_div_rcp2(make_float2(bf16lo_to_f32(w[i]), bf16hi_to_f32(w[i])), nscale2, rcp2,
+                                         c[2 * i], c[2 * i + 1]);
                 uint2 o2;
-                o2.x = pack_lowbytes(quant_trunc_div_rcp(e[0], scale, rcp), quant_trunc_div_rcp(e[1], scale, rcp),
-                                     quant_trunc_div_rcp(e[2], scale, rcp), quant_trunc_div_rcp(e[3], scale, rcp));
-                o2.y = pack_lowbytes(quant_trunc_div_rcp(e[4], scale, rcp), quant_trunc_div_rcp(e[5], scale, rcp),
-                                     quant_trunc_div_rcp(e[6], scale, rcp), quant_trunc_div_rcp(e[7], scale, rcp));
+                o2.x = pack_lowbytes(c[0], c[1], c[2], c[3]);
+                o2.y = pack_lowbytes(c[4], c[5], c[6], c[7]);
                 q[f] = o2;
             }
         }
@@ -474,7 +477,7 @@ __global__ void __launch_bounds__(T, MINB) silu_mul_quant_table_kernel(
     const int V = N >> 3, tid = threadIdx.x;
     if (valid_rows != nullptr) M = min(M, __ldg(valid_rows));
     if ((int)blockIdx.x >= M) return;
-    for (int i = tid; i < kSigTabEntries; i += T) tab[i] = sigmoid_table_entry(i);
+    for (int i = tid; i < kSigTabEntries; i += T) tab[i] = silu_table_entry(i);
     __syncthreads();
     for (int row = blockIdx.x; row < M; row += gridDim.x) {
         if (mask != nullptr && mask[row] == 0) continue;  // uniform over the block
@@ -531,11 +534,12 @@ __global__ void __launch_bounds__(T, MINB) silu_mul_quant_table_kernel(
 // Persistent form used for many rows.  One CTA of 1024 threads per SM = two independent groups of
 // 512 threads that share the sigmoid table.  Each group owns a shared-memory row buffer and walks
 // its own row blocks (RPB rows of N gates + N ups each):
-//   wait (mbarrier) for the block's bulk copies -> h = silu(g)*u from shared memory into registers
-//   -> group barrier (also publishes the per-warp maxima) -> one thread starts the bulk copies of
-//   the group's NEXT block into the same buffer -> row maximum, quantise, store.
+//   wait (mbarrier) for the block's bulk copies -> the thread's gates and ups from shared memory
+//   into registers -> group barrier -> one thread starts the bulk copies of the group's NEXT block
+//   into the same buffer -> h = silu(g)*u in registers -> group barrier (publishes the per-warp
+//   maxima) -> row maximum, quantise, store.
 // The copies (cp.async.bulk, one per half row, completion counted on an mbarrier) therefore overlap
-// the reduce / quantise / store part of the same group and everything the other group does, keep a
+// all the arithmetic and the stores of the same group and everything the other group does, keep a
 // whole row block in flight per group without registers or load/store-unit request slots, and the
 // two groups are in different phases most of the time, so the shared-memory pipe (table gathers)
 // and the arithmetic pipes (quantisation) are busy together.
@@ -564,6 +568,8 @@ __global__ void __launch_bounds__(1024, 1) silu_mul_quant_async_kernel(
     const uint32_t bar = ptx::smem_u32(&bars[grp]);
     const uint32_t half_bytes = (uint32_t)N * 2u;  // one row of gates (or ups) in bf16
     uint4* my_buf = smem4 + (size_t)(grp * RPB) * 2 * V;
+    // 1.0f that the compiler cannot see through (N is positive): see quant_rn_lowbyte2
+    const float2 one2 = splat2(__int_as_float(0x3f800000 | (N >> 31)));
 
     auto row_active = [&](int row) { return row < M && (mask == nullptr || mask[row] != 0); };
     // the group's first thread: arm the barrier with the bytes to come and start the copies.  The
@@ -587,7 +593,7 @@ __global__ void __launch_bounds__(1024, 1) silu_mul_quant_async_kernel(
         ptx::fence_barrier_init();
         if (first < nblocks) issue(first);
     }
-    for (int i = tid; i < kSigTabEntries; i += 1024) tab[i] = sigmoid_table_entry(i);
+    for (int i = tid; i < kSigTabEntries; i += 1024) tab[i] = silu_table_entry(i);
     __syncthreads();  // table complete, barriers initialised
 
     uint32_t it = 0;
@@ -600,23 +606,44 @@ __global__ void __launch_bounds__(1024, 1) silu_mul_quant_async_kernel(
         const bool active = row_active(row);
         const uint4* gb = my_buf + (size_t)(gi * 2) * V;
         const uint4* ub = gb + V;
-        float2 h[VPT][4];
+        // the thread's share of the row block goes to registers first, so that the buffer is free
+        // and the next block's copies start before any arithmetic on this one; h later replaces
+        // the raw words in the same registers
+        uint32_t r[VPT][8];
+        if (active) {
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int idx = lt + j * GT;
+                if (idx < V) {
+                    const uint4 gv = gb[idx], uv = ub[idx];
+                    r[j][0] = gv.x; r[j][1] = gv.y; r[j][2] = gv.z; r[j][3] = gv.w;
+                    r[j][4] = uv.x; r[j][5] = uv.y; r[j][6] = uv.z; r[j][7] = uv.w;
+                }
+            }
+        }
+        group_barrier(1 + grp, GROUP);  // the buffer has been read by everyone
+        if (gtid == 0 && rb + stride < nblocks) issue(rb + stride);
         float am = 0.0f;
         if (active) {
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
                 const int idx = lt + j * GT;
                 if (idx < V) {
-                    silu_mul8_table(gb[idx], ub[idx], tab, h[j]);
-                    am = fmaxf(am, fmaxf(fmaxf(fabsf(h[j][0].x), fabsf(h[j][0].y)), fmaxf(fabsf(h[j][1].x), fabsf(h[j][1].y))));
-                    am = fmaxf(am, fmaxf(fmaxf(fabsf(h[j][2].x), fabsf(h[j][2].y)), fmaxf(fabsf(h[j][3].x), fabsf(h[j][3].y))));
+                    float2 h[4];
+                    silu_mul8_table(make_uint4(r[j][0], r[j][1], r[j][2], r[j][3]),
+                                    make_uint4(r[j][4], r[j][5], r[j][6], r[j][7]), tab, h);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        am = max3_abs(am, h[i].x, h[i].y);
+                        r[j][2 * i] = __float_as_uint(h[i].x);
+                        r[j][2 * i + 1] = __float_as_uint(h[i].y);
+                    }
                 }
             }
         }
         am = warp_max(am);
         if (lane == 0) red[grp][it & 1u][gi][wig] = am;
-        group_barrier(1 + grp, GROUP);  // the buffer has been read by everyone; the maxima are visible
-        if (gtid == 0 && rb + stride < nblocks) issue(rb + stride);
+        group_barrier(3 + grp, GROUP);  // the per-warp maxima are visible
         float rowmax = (lane < WPG) ? red[grp][it & 1u][gi][lane] : 0.0f;
         rowmax = warp_max(rowmax);
         if (active) {
@@ -629,10 +656,12 @@ __global__ void __launch_bounds__(1024, 1) silu_mul_quant_async_kernel(
             for (int j = 0; j < VPT; ++j) {
                 const int idx = lt + j * GT;
                 if (idx < V) {
-                    const float2 c0 = quant_rn_lowbyte2(h[j][0], inv2);
-                    const float2 c1 = quant_rn_lowbyte2(h[j][1], inv2);
-                    const float2 c2 = quant_rn_lowbyte2(h[j][2], inv2);
-                    const float2 c3 = quant_rn_lowbyte2(h[j][3], inv2);
+                    float2 c[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        c[i] = quant_rn_lowbyte2(make_float2(__uint_as_float(r[j][2 * i]), __uint_as_float(r[j][2 * i + 1])),
+                                                 inv2, one2);
+                    const float2 c0 = c[0], c1 = c[1], c2 = c[2], c3 = c[3];
                     uint2 o;
                     o.x = pack_lowbytes(__float_as_uint(c0.x), __float_as_uint(c0.y), __float_as_uint(c1.x), __float_as_uint(c1.y));
                     o.y = pack_lowbytes(__float_as_uint(c2.x), __float_as_uint(c2.y), __float_as_uint(c3.x), __float_as_uint(c3.y));

@@ -87,6 +87,28 @@ __device__ __forceinline__ uint32_t quant_trunc_div_rcp(float x, float scale, fl
     return (uint32_t)__float2int_rz(q1);
 }
 
+// Two elements at once with the packed f32x2 instructions (same three roundings per element).
+// nscale2 holds -scale in both halves: the packed fma has no negate modifier.
+__device__ __forceinline__ void quant_trunc_div_rcp2(float2 x, float2 nscale2, float2 rcp2, uint32_t& lo,
+                                                     uint32_t& hi) {
+    const float2 q0 = __fmul2_rn(x, rcp2);
+    const float2 r = __ffma2_rn(q0, nscale2, x);
+    const float2 q1 = __ffma2_rn(r, rcp2, q0);
+    lo = (uint32_t)__float2int_rz(q1.x);
+    hi = (uint32_t)__float2int_rz(q1.y);
+}
+
+// RN(a / 127) without the division routine, for a >= kAmaxFloor: q0 = RN(a * RN(1/127)) is within
+// one ulp of the quotient, the remainder a - 127*q0 is exact in one fma, and the corrected quotient
+// rounds correctly (the same closing step as above).  Checked against __fdiv_rn for every bf16
+// magnitude in the GPU tests.
+constexpr float kRcp127 = 1.0f / 127.0f;   // correctly rounded: 0x3C010204
+__device__ __forceinline__ float div127_rn(float a) {
+    const float q0 = __fmul_rn(a, kRcp127);
+    const float r = __fmaf_rn(q0, -127.0f, a);
+    return __fmaf_rn(r, kRcp127, q0);
+}
+
 __device__ __forceinline__ uint32_t pack_i8x4(int a, int b, int c, int d) {
     return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) |
            ((uint32_t)(d & 0xff) << 24);
@@ -136,26 +158,22 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
     return __fmul_rn(__fmul_rn(sigmoid_fixed(g), g), u);
 }
 
-// ---- sigmoid by table -------------------------------------------------------------------
-// The gate is bf16: only 65536 inputs exist.  A kernel may tabulate sigmoid_fixed for the
-// inputs with 2^-12 <= |g| < 16 (2048 bit patterns per sign, 4096 floats = 16 KB of shared
+// ---- silu by table ------------------------------------------------------------------------
+// The gate is bf16: only 65536 inputs exist.  A kernel may tabulate silu(g) = RN(sigmoid_fixed(g)*g)
+// for the inputs with 2^-12 <= |g| < 16 (2048 bit patterns per sign, 4096 floats = 16 KB of shared
 // memory) and look values up instead of recomputing them; inputs outside that range (zeros,
-// tiny, huge, NaN) take sigmoid_fixed directly.  The table holds sigmoid_fixed's own results,
-// so a lookup returns exactly what the computation would.
+// tiny, huge, NaN) are computed.  The table holds the computation's own results, so a lookup
+// returns exactly the same bits.
 constexpr uint32_t kSigTabLo = 0x3980u;    // bf16 bits of 2^-12
-constexpr int kSigTabEntries = 4096;       // [sign][(|g| bits) - kSigTabLo]
+constexpr int kSigTabEntries = 4096;
 
-__device__ __forceinline__ float sigmoid_table_entry(int i) {
-    const uint32_t bits = ((uint32_t)(i >> 11) << 15) | (kSigTabLo + (uint32_t)(i & 0x7ff));
-    return sigmoid_fixed(__uint_as_float(bits << 16));
-}
-
-// Index arithmetic: t = (bf16 bits - kSigTabLo) mod 2^16 is a table hit iff bits 11..14 are
-// clear (bit 15 is the sign); the entry is (t & 0x7ff) | (sign << 11).
-__device__ __forceinline__ uint32_t sig_t_lo(uint32_t gw) { return (gw - kSigTabLo) & 0xffffu; }
-__device__ __forceinline__ uint32_t sig_t_hi(uint32_t gw) { return ((gw >> 16) - kSigTabLo) & 0xffffu; }
-__device__ __forceinline__ float sig_entry(uint32_t t, const float* __restrict__ tab) {
-    return tab[(t & 0x7ffu) | ((t >> 4) & 0x800u)];
+// Entry i < 2048 holds silu(g) = RN(sigmoid_fixed(g) * g) for the positive gate with bf16 bits
+// kSigTabLo + i; entry i >= 2048 the negative gate with magnitude bits kSigTabLo + (4095 - i).
+// With t = gate bits - kSigTabLo (mod 2^16) that is entry (t ^ (sign ? 0xffff : 0)) & 0xfff.
+__device__ __forceinline__ float silu_table_entry(int i) {
+    const uint32_t bits = i < 2048 ? (kSigTabLo + (uint32_t)i) : (0x8000u | (kSigTabLo + (uint32_t)(4095 - i)));
+    const float g = __uint_as_float(bits << 16);
+    return __fmul_rn(sigmoid_fixed(g), g);
 }
 
 // ---- two-lane forms ------------------------------------------------------------------
@@ -201,25 +219,51 @@ __device__ __forceinline__ float2 quant_rn_lowbyte2(float2 x, float2 inv2) {
     return make_float2(__fadd_rn(__fmul_rn(x.x, inv2.x), kRoundMagic), __fadd_rn(__fmul_rn(x.y, inv2.y), kRoundMagic));
 }
 
-// h for the 8 gates / ups of one 16-byte vector pair.  One range test for the whole vector: if
-// all 8 gates hit the table the values are looked up, otherwise (rare: zeros, tiny or huge
-// gates) the whole vector is computed.  Both give sigmoid_fixed's value.
+// The same rounding sequence with the packed instructions: RN(x*inv) by the packed multiply, then
+// the magic constant added by a packed fma whose multiplier `one2` is 1.0 taken from a run-time
+// value, so the assembler sees an ordinary fma of an already rounded product and cannot merge the
+// two steps.  RN(p * 1 + magic) = RN(p + magic).
+__device__ __forceinline__ float2 quant_rn_lowbyte2(float2 x, float2 inv2, float2 one2) {
+    return __ffma2_rn(__fmul2_rn(x, inv2), one2, splat2(kRoundMagic));
+}
+
+// max(a, |b|, |c|) in one instruction (three-input max of sm_100)
+__device__ __forceinline__ float max3_abs(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(fabsf(b)), "f"(fabsf(c)));
+    return d;
+}
+
+// 0xffffffff if bit 15 of w is set, else 0: prmt with the sign-replicate flag (selector nibble 8 | 1)
+// on all four result bytes.
+__device__ __forceinline__ uint32_t sign_of_byte1(uint32_t w) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, 0x9999;" : "=r"(d) : "r"(w), "r"(0u));
+    return d;
+}
+
+// h for the 8 gates / ups of one 16-byte vector pair; tab is the silu table.
+// Both halves of a word are rebased with one subtraction (a borrow out of the low half only happens
+// for a low gate below the table, which is a miss anyway) and one range test covers the vector:
+// a gate hits iff bits 11..14 of its rebased pattern are clear (bit 15 is the sign).  If all 8
+// gates hit, silu(g) is looked up, otherwise (rare: zeros, tiny or huge gates) the whole vector is
+// computed.  Both give the same bits.
 __device__ __forceinline__ void silu_mul8_table(const uint4& gv, const uint4& uv, const float* __restrict__ tab,
                                                 float2 (&h)[4]) {
     const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
-    uint32_t t[8];
-    uint32_t miss = 0;
+    constexpr uint32_t kRebase = kSigTabLo | (kSigTabLo << 16);
+    uint32_t t[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        t[2 * i] = sig_t_lo(gw[i]);
-        t[2 * i + 1] = sig_t_hi(gw[i]);
-        miss |= t[2 * i] | t[2 * i + 1];
-    }
-    if ((miss & 0x7800u) == 0) {
+    for (int i = 0; i < 4; ++i) t[i] = gw[i] - kRebase;
+    if (((t[0] | t[1] | t[2] | t[3]) & 0x78007800u) == 0) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const float2 sig = make_float2(sig_entry(t[2 * i], tab), sig_entry(t[2 * i + 1], tab));
-            h[i] = __fmul2_rn(__fmul2_rn(sig, bf16x2_to_f32x2(gw[i])), bf16x2_to_f32x2(uw[i]));
+            // the index is masked to the table's 4096 entries whatever the gate bits are
+            const uint32_t sign_lo = sign_of_byte1(t[i]);
+            const uint32_t sign_hi = (uint32_t)((int)t[i] >> 31);
+            const uint32_t lo = (t[i] ^ sign_lo) & 0xfffu;
+            const uint32_t hi = ((t[i] >> 16) ^ sign_hi) & 0xfffu;
+            h[i] = __fmul2_rn(make_float2(tab[lo], tab[hi]), bf16x2_to_f32x2(uw[i]));
         }
     } else {
 #pragma unroll

@@ -256,6 +256,23 @@ def test_ptgq_many_elements_and_exact_multiples(cabi):
     _eq(q, q_ref, "codes (multiples)")
 
 
+def test_ptgq_scale_for_every_bf16_amax(cabi):
+    # the vector kernel forms amax/127 from a reciprocal and one correction step: every finite
+    # positive bf16 value as a group's amax must give the bits of the true division
+    bits = torch.arange(1, 0x7F80, dtype=torch.int32)             # all finite positive bf16 patterns
+    vals = bits.to(torch.int16).view(torch.bfloat16)
+    pad = (-len(vals)) % 56
+    vals = torch.cat([vals, vals[:pad]])
+    x = torch.zeros(len(vals), 128, dtype=torch.bfloat16)
+    x[:, 5] = vals
+    x[1::2, 77] = -vals[1::2]
+    x = x.reshape(-1, 56 * 128).contiguous()
+    q_ref, s_ref = oracle.per_token_group_quant_int8(x, 128)
+    q, s = cabi.ptgq(x.cuda(), 128)
+    _eq(s, s_ref, "scales")
+    _eq(q, q_ref, "codes")
+
+
 def test_silu_mul_quant_many_rows_with_mask_and_row_count(cabi, ext):
     # the persistent kernels with a row mask and with a device-side row count
     m, n = 700, 18432
