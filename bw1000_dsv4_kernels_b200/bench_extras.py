@@ -173,6 +173,19 @@ def _moe_section(ext, dev, rank, world, peaks, time_launches):
             "weight_hbm_frac": round(w_bytes / (ms_local * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
             "experts_per_rank": hi - lo, "ranks": world,
         }
+        if world > 1:
+            # combine fused with the exchange over peer memory instead of fp32 partials + all-reduce
+            try:
+                ex = moe.ExchangeW8A8MoE(inp.w13, inp.w13_scale, inp.w2, inp.w2_scale, E, rank, world, t_max=T,
+                                         topk=topk, device=dev, group_scaled=gs)
+                _sync(world)
+                ms_ex = _max_over_ranks(time_launches(lambda i: ex.forward(inp.x, inp.topk_ids, inp.topk_w), 10, warmup=2),
+                                        dev, world)
+                out[name]["ms_with_fused_exchange"] = round(ms_ex, 4)
+                out[name]["TOPS_whole_job_fused_exchange"] = round(ops / (ms_ex * 1e-3) / 1e12, 1)
+                del ex
+            except Exception as exc:  # pragma: no cover
+                out[name]["fused_exchange_error"] = f"{type(exc).__name__}: {exc}"
     # stage breakdown of the group-scaled chain on this rank
     layer = moe.W8A8MoE(inp.w13, inp.w13_scale, inp.w2, inp.w2_scale, E, expert_lo=lo, group_scaled=True)
     layer.local_partial(inp.x, inp.topk_ids, inp.topk_w, out_f32=False, keep_trace=True)

@@ -187,6 +187,13 @@ int launch_moe_combine(const void* z, const int* dst_slot, const float* topk_w, 
     return moe_combine(z, dst_slot, topk_w, out, T, topk, H, out_f32, cs(stream));
 }
 
+int launch_moe_combine_exchange(const void* const* z_ranks, const int* const* slot_ranks, const int* topk_ids,
+                                const float* topk_w, void* const* out_ranks, int num_ranks, int experts_per_rank,
+                                int t0, int t1, int topk, int H, dsv4_stream_t stream) {
+    return moe_combine_exchange(z_ranks, slot_ranks, topk_ids, topk_w, out_ranks, num_ranks, experts_per_rank, t0, t1,
+                                topk, H, cs(stream));
+}
+
 int launch_w8a8_gemm_allgather(const void* A, const void* B, const void* sa, const void* sb, void* C_local,
                                void* const* C_peers, int npeers, int64_t ldc, int M, int N, int K,
                                dsv4_stream_t stream) {

@@ -254,6 +254,96 @@ __global__ void __launch_bounds__(128) moe_combine_kernel(const __nv_bfloat16* _
     }
 }
 
+// Expert-parallel combine fused with its exchange.  Every rank holds the outputs of its own experts
+// (z, rows in its own segment order) and its own dst_slot map; all ranks' buffers are mapped into
+// this GPU's address space.  The rank that owns token t pulls the token's top-k expert rows from
+// whichever ranks hold them (peer loads), sums them in slot order with the same fp32 fma sequence as
+// moe_combine -- so the result has the single-GPU bits -- and pushes the bf16 row into every rank's
+// output (peer stores).  Per rank about T/G * topk rows come in and T/G * (G-1) rows go out, against
+// an all-reduce of fp32 [T,H] partials.
+constexpr int kMaxRanks = 8;
+struct ExchangeArgs {
+    const __nv_bfloat16* z[kMaxRanks];
+    const int* slot[kMaxRanks];
+    __nv_bfloat16* out[kMaxRanks];
+};
+
+__global__ void __launch_bounds__(128) moe_combine_exchange_kernel(ExchangeArgs a, const int* __restrict__ ids,
+                                                                   const float* __restrict__ w, int G,
+                                                                   int experts_per_rank, int t0, int t1, int topk,
+                                                                   int H) {
+    constexpr int kBatch = 8;                   // expert rows in flight per thread
+    __shared__ const uint4* rowp[kBatch];
+    __shared__ float wk[kBatch];
+    const int V = H >> 3;
+    for (int t = t0 + blockIdx.x; t < t1; t += gridDim.x) {
+        float acc[4][8];                        // up to four 16-byte vectors per thread and pass
+        for (int vb = 0; vb < V; vb += 4 * 128) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[i][e] = 0.0f;
+            for (int j0 = 0; j0 < topk; j0 += kBatch) {
+                __syncthreads();                // the previous batch's pointers have been used
+                if (threadIdx.x < kBatch) {
+                    const int j = j0 + threadIdx.x;
+                    const uint4* ptr = nullptr;
+                    float wj = 0.0f;
+                    if (j < topk) {
+                        const int64_t pair = (int64_t)t * topk + j;
+                        const int e = __ldg(ids + pair);
+                        const int rank = e >= 0 ? e / experts_per_rank : G;
+                        wj = __ldg(w + pair);
+#pragma unroll
+                        for (int r = 0; r < kMaxRanks; ++r) {
+                            if (r == rank && r < G) {
+                                const int slot = a.slot[r][pair];
+                                if (slot >= 0) ptr = reinterpret_cast<const uint4*>(a.z[r] + (int64_t)slot * H);
+                            }
+                        }
+                    }
+                    rowp[threadIdx.x] = ptr;
+                    wk[threadIdx.x] = wj;
+                }
+                __syncthreads();
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int v = vb + i * 128 + threadIdx.x;
+                    if (v >= V) break;
+                    uint4 zv[kBatch];
+#pragma unroll
+                    for (int j = 0; j < kBatch; ++j)
+                        zv[j] = rowp[j] != nullptr ? rowp[j][v] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                    for (int j = 0; j < kBatch; ++j) {
+                        if (rowp[j] == nullptr) continue;   // a skipped slot adds nothing, not even +0
+                        const float wj = wk[j];
+                        const uint32_t zw[4] = {zv[j].x, zv[j].y, zv[j].z, zv[j].w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            acc[i][2 * e] = __fmaf_rn(wj, __uint_as_float(zw[e] << 16), acc[i][2 * e]);
+                            acc[i][2 * e + 1] = __fmaf_rn(wj, __uint_as_float(zw[e] & 0xffff0000u), acc[i][2 * e + 1]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int v = vb + i * 128 + threadIdx.x;
+                if (v >= V) break;
+                __nv_bfloat162 b[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) b[e] = __floats2bfloat162_rn(acc[i][2 * e], acc[i][2 * e + 1]);
+                const uint4 packed = *reinterpret_cast<uint4*>(b);
+#pragma unroll
+                for (int r = 0; r < kMaxRanks; ++r)
+                    if (r < G) reinterpret_cast<uint4*>(a.out[r] + (int64_t)t * H)[v] = packed;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // Router top-k: one warp per token.  Lane l holds logits l, l+32, ...; k rounds of a warp-wide
 // arg-max (larger value wins, ties go to the lower expert index) pick the experts in descending
 // order; the weights are the softmax over the k selected logits (exp computed in fp32 with the
@@ -326,6 +416,29 @@ int moe_combine(const void* z, const int* dst_slot, const float* w, void* out, i
     else
         moe_combine_kernel<false><<<T, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(z), dst_slot, w, out, T, topk, H);
     return check_launch("moe_combine");
+}
+
+int moe_combine_exchange(const void* const* z_ranks, const int* const* slot_ranks, const int* topk_ids,
+                         const float* topk_w, void* const* out_ranks, int G, int experts_per_rank, int t0, int t1,
+                         int topk, int H, cudaStream_t st) {
+    if (t1 <= t0 || H == 0) return 0;
+    if (G < 1 || G > kMaxRanks) return fail(DSV4_ERR_ARG, "moe_combine_exchange: 1 to 8 ranks");
+    if (t0 < 0 || topk <= 0 || experts_per_rank <= 0 || H < 0 || H % 8 != 0)
+        return fail(DSV4_ERR_ARG, "moe_combine_exchange: bad sizes (H must be a multiple of 8)");
+    if (z_ranks == nullptr || slot_ranks == nullptr || out_ranks == nullptr || topk_ids == nullptr || topk_w == nullptr)
+        return fail(DSV4_ERR_ARG, "moe_combine_exchange: null pointer");
+    ExchangeArgs a = {};
+    for (int r = 0; r < G; ++r) {
+        if (z_ranks[r] == nullptr || slot_ranks[r] == nullptr || out_ranks[r] == nullptr)
+            return fail(DSV4_ERR_ARG, "moe_combine_exchange: null rank pointer");
+        if ((reinterpret_cast<uintptr_t>(z_ranks[r]) & 15) || (reinterpret_cast<uintptr_t>(out_ranks[r]) & 15))
+            return fail(DSV4_ERR_ARG, "moe_combine_exchange: z and out must be 16-byte aligned");
+        a.z[r] = static_cast<const __nv_bfloat16*>(z_ranks[r]);
+        a.slot[r] = slot_ranks[r];
+        a.out[r] = static_cast<__nv_bfloat16*>(out_ranks[r]);
+    }
+    moe_combine_exchange_kernel<<<t1 - t0, 128, 0, st>>>(a, topk_ids, topk_w, G, experts_per_rank, t0, t1, topk, H);
+    return check_launch("moe_combine_exchange");
 }
 
 int moe_segments(const int* topk_ids, int T, int topk, int E, int expert_lo, int* offsets, int* src_row,

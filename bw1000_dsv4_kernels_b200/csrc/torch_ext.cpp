@@ -247,7 +247,8 @@ Tensor scale_convert_stream(Tensor acc, Tensor sa, Tensor sb, int64_t stream_ptr
 }
 
 // ---- grouped_gemm ------------------------------------------------------------------
-Tensor grouped_gemm_stream(Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor expert_offsets, int64_t stream_ptr) {
+Tensor grouped_gemm_impl(Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor expert_offsets, c10::optional<Tensor> out,
+                         int64_t stream_ptr) {
     check_cuda(A, "A", torch::kInt8);
     check_cuda(W, "W", torch::kInt8);
     check_cuda(sa, "sa", torch::kFloat32);
@@ -270,14 +271,33 @@ Tensor grouped_gemm_stream(Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor expe
         groups = K / 128;
     }
     c10::cuda::CUDAGuard guard(A.device());
-    auto C = torch::empty({R, N}, A.options().dtype(torch::kBFloat16));
+    Tensor C;
+    if (out.has_value()) {   // e.g. a buffer in symmetric memory that peers read
+        C = *out;
+        check_cuda(C, "out", torch::kBFloat16);
+        TORCH_CHECK(C.dim() == 2 && C.is_contiguous() && C.size(0) >= R && C.size(1) == N,
+                    "out must be a contiguous bf16 [>= R, N] tensor");
+    } else {
+        C = torch::empty({R, N}, A.options().dtype(torch::kBFloat16));
+    }
     check_status(launch_grouped_gemm(A.data_ptr(), W.data_ptr(), sa_c.data_ptr(), sw.data_ptr(),
                                      static_cast<const int*>(expert_offsets.data_ptr()), C.data_ptr(), R, E, N, K,
                                      groups, as_stream(stream_ptr)));
     return C;
 }
 
+Tensor grouped_gemm_stream(Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor expert_offsets, int64_t stream_ptr) {
+    return grouped_gemm_impl(A, W, sa, sw, expert_offsets, c10::nullopt, stream_ptr);
+}
+
+std::vector<Tensor> moe_segments_impl(Tensor topk_ids, int64_t num_experts, int64_t expert_lo,
+                                      c10::optional<Tensor> slot_out, int64_t stream_ptr);
 std::vector<Tensor> moe_segments_stream(Tensor topk_ids, int64_t num_experts, int64_t expert_lo, int64_t stream_ptr) {
+    return moe_segments_impl(topk_ids, num_experts, expert_lo, c10::nullopt, stream_ptr);
+}
+
+std::vector<Tensor> moe_segments_impl(Tensor topk_ids, int64_t num_experts, int64_t expert_lo,
+                                      c10::optional<Tensor> slot_out, int64_t stream_ptr) {
     check_cuda(topk_ids, "topk_ids", torch::kInt32);
     TORCH_CHECK(topk_ids.dim() == 2 && topk_ids.is_contiguous(), "topk_ids must be a contiguous [T,topk] tensor");
     c10::cuda::CUDAGuard guard(topk_ids.device());
@@ -285,7 +305,15 @@ std::vector<Tensor> moe_segments_stream(Tensor topk_ids, int64_t num_experts, in
     auto opt = topk_ids.options();
     auto offsets = torch::empty({num_experts + 1}, opt);
     auto src_row = torch::empty({(int64_t)T * topk}, opt);
-    auto dst_slot = torch::empty({(int64_t)T * topk}, opt);
+    Tensor dst_slot;
+    if (slot_out.has_value()) {   // e.g. a buffer in symmetric memory that peers read
+        check_cuda(*slot_out, "dst_slot", torch::kInt32);
+        TORCH_CHECK(slot_out->is_contiguous() && slot_out->numel() >= (int64_t)T * topk,
+                    "dst_slot must be a contiguous int32 tensor with at least T*topk entries");
+        dst_slot = slot_out->view({-1}).narrow(0, 0, (int64_t)T * topk);
+    } else {
+        dst_slot = torch::empty({(int64_t)T * topk}, opt);
+    }
     if (T == 0) {
         offsets.zero_();
         return {offsets, src_row, dst_slot};
@@ -362,6 +390,34 @@ Tensor moe_combine_stream(Tensor z, Tensor dst_slot, Tensor topk_w, bool out_f32
                                     static_cast<const float*>(topk_w.data_ptr()), out.data_ptr(), T, topk, H,
                                     out_f32 ? 1 : 0, as_stream(stream_ptr)));
     return out;
+}
+
+// Expert-parallel combine + exchange: pointers (as integers) to every rank's z, dst_slot and out
+// buffers, mapped into this GPU's address space (symmetric memory buffer_ptrs); tokens [t0, t1).
+void moe_combine_exchange_stream(std::vector<int64_t> z_ptrs, std::vector<int64_t> slot_ptrs, Tensor topk_ids,
+                                 Tensor topk_w, std::vector<int64_t> out_ptrs, int64_t experts_per_rank, int64_t t0,
+                                 int64_t t1, int64_t H, int64_t stream_ptr) {
+    check_cuda(topk_ids, "topk_ids", torch::kInt32);
+    check_cuda(topk_w, "topk_w", torch::kFloat32);
+    TORCH_CHECK(topk_ids.dim() == 2 && topk_ids.is_contiguous() && topk_w.is_contiguous() &&
+                topk_w.sizes() == topk_ids.sizes(), "topk_ids and topk_w must be contiguous [T,topk]");
+    const size_t G = z_ptrs.size();
+    TORCH_CHECK(G >= 1 && G <= 8 && slot_ptrs.size() == G && out_ptrs.size() == G, "1 to 8 ranks, three pointer lists");
+    TORCH_CHECK(t0 >= 0 && t1 <= topk_ids.size(0), "token range outside [0, T)");
+    c10::cuda::CUDAGuard guard(topk_ids.device());
+    std::vector<const void*> z(G);
+    std::vector<const int*> slot(G);
+    std::vector<void*> out(G);
+    for (size_t r = 0; r < G; ++r) {
+        z[r] = reinterpret_cast<const void*>(z_ptrs[r]);
+        slot[r] = reinterpret_cast<const int*>(slot_ptrs[r]);
+        out[r] = reinterpret_cast<void*>(out_ptrs[r]);
+    }
+    check_status(launch_moe_combine_exchange(z.data(), slot.data(), static_cast<const int*>(topk_ids.data_ptr()),
+                                             static_cast<const float*>(topk_w.data_ptr()), out.data(), (int)G,
+                                             to_int(experts_per_rank, "experts_per_rank"), to_int(t0, "t0"),
+                                             to_int(t1, "t1"), to_int(topk_ids.size(1), "topk"), to_int(H, "H"),
+                                             as_stream(stream_ptr)));
 }
 
 // w8a8 GEMM written into columns [col0, col0 + N) of an existing bf16 [M, ldc] buffer
@@ -449,6 +505,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         return grouped_gemm_stream(A, W, sa, sw, off, current_stream_ptr());
     });
     m.def("grouped_gemm_stream", &grouped_gemm_stream);
+    m.def("grouped_gemm_into", [](Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor off, Tensor out) {
+        return grouped_gemm_impl(A, W, sa, sw, off, out, current_stream_ptr());
+    });
+    m.def("moe_segments_into", [](Tensor ids, int64_t E, int64_t lo, Tensor slot_out) {
+        return moe_segments_impl(ids, E, lo, slot_out, current_stream_ptr());
+    });
+    m.def("moe_combine_exchange", [](std::vector<int64_t> z, std::vector<int64_t> slot, Tensor ids, Tensor w,
+                                     std::vector<int64_t> out, int64_t epr, int64_t t0, int64_t t1, int64_t H) {
+        moe_combine_exchange_stream(z, slot, ids, w, out, epr, t0, t1, H, current_stream_ptr());
+    });
+    m.def("moe_combine_exchange_stream", &moe_combine_exchange_stream);
     m.def("moe_segments", [](Tensor ids, int64_t E, int64_t lo) {
         return moe_segments_stream(ids, E, lo, current_stream_ptr());
     }, py::arg("topk_ids"), py::arg("num_experts"), py::arg("expert_lo") = 0);

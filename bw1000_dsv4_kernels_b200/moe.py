@@ -16,10 +16,13 @@ the number of routed rows of a rank stays on the device (expert_offsets[-1]) and
 that walk rows take it from there.
 
 Expert parallelism: rank r owns experts [r*E/G, (r+1)*E/G).  Tokens and routing are replicated
-(every rank computes the same top-k from the same logits), each rank runs the chain for its own
-experts and produces an fp32 partial [T,H]; one NCCL all-reduce sums the partials.  The sum over
-ranks associates differently from the single-GPU sum, so the bf16 result agrees to rounding, not
-bit for bit; integer codes, scales and accumulators per expert are identical.
+(every rank computes the same top-k from the same logits) and each rank runs the chain for its own
+experts.  Two ways to put the rows together:
+  * W8A8MoE: every rank produces an fp32 partial [T,H]; one NCCL all-reduce sums the partials.  The
+    sum over ranks associates differently from the single-GPU sum, so the bf16 result agrees to
+    rounding, not bit for bit; integer codes, scales and accumulators per expert are identical.
+  * ExchangeW8A8MoE: the combine pulls the expert rows from peer memory and pushes the finished bf16
+    rows to every rank in one kernel; the result is bit-identical to the single-GPU forward.
 """
 from dataclasses import dataclass
 from typing import Optional
@@ -96,6 +99,68 @@ class W8A8MoE:
         if self.pg is not None or dist.is_initialized():
             dist.all_reduce(part, group=self.pg)
         return part.to(torch.bfloat16)
+
+
+def token_range(rank: int, world: int, tokens: int):
+    """Tokens [t0, t1) whose output rows `rank` produces in the fused combine (contiguous blocks)."""
+    per = (tokens + world - 1) // world
+    return min(tokens, rank * per), min(tokens, (rank + 1) * per)
+
+
+class ExchangeW8A8MoE(W8A8MoE):
+    """Expert-parallel forward whose combine is fused with the exchange (`moe_combine_exchange`).
+
+    The down GEMM writes this rank's expert outputs z and `moe_segments` its slot map into symmetric
+    memory (every rank's buffers are mapped into every other rank's address space).  After a barrier
+    on the stream, the rank that owns a token pulls the token's top-k rows from the ranks that hold
+    them over NVLink, sums them in slot order -- the single-GPU arithmetic, so the bf16 result is
+    bit-identical to the one-GPU forward whatever the number of ranks -- and pushes the row into every
+    rank's output buffer.  A second barrier makes the rows visible.  No NCCL call on the data path and
+    no fp32 [T,H] partials: per rank about T/G*topk rows come in and T/G*(G-1) rows go out.
+    """
+
+    def __init__(self, w13, w13_scale, w2, w2_scale, num_experts: int, rank: int, world: int, t_max: int, topk: int,
+                 device, group_scaled: bool = True, process_group=None):
+        per = num_experts // world
+        assert per * world == num_experts and w13.shape[0] == per
+        super().__init__(w13, w13_scale, w2, w2_scale, num_experts, rank * per, group_scaled, process_group)
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        self.rank, self.world, self.t_max, self.topk = rank, world, t_max, topk
+        group = process_group if process_group is not None else dist.group.WORLD
+        self.z = symm_mem.empty((t_max * topk, self.hidden), dtype=torch.bfloat16, device=device)
+        self.slots = symm_mem.empty((t_max * topk,), dtype=torch.int32, device=device)
+        self.out = symm_mem.empty((t_max, self.hidden), dtype=torch.bfloat16, device=device)
+        self.handle = symm_mem.rendezvous(self.z, group=group)
+        self.z_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.slot_ptrs = [int(p) for p in symm_mem.rendezvous(self.slots, group=group).buffer_ptrs]
+        self.out_ptrs = [int(p) for p in symm_mem.rendezvous(self.out, group=group).buffer_ptrs]
+
+    def local_rows(self, x, topk_ids):
+        """This rank's experts up to the down GEMM: z and the slot map land in symmetric memory."""
+        ext = _ext()
+        inter = self.inter
+        if self.group_scaled:
+            q, s = ext.per_token_group_quant_int8(x, GROUP)
+        else:
+            q, s = ext.per_token_quant_int8(x)
+        off, src_row, _ = ext.moe_segments_into(topk_ids, self.e_local, self.expert_lo, self.slots)
+        valid = off[self.e_local:]
+        a_q, a_s = ext.gather_rows(q, src_row, s, valid)
+        y = ext.grouped_gemm(a_q, self.w13, a_s, self.w13_scale, off)
+        h_q, h_s = ext.silu_mul_quant_rows(y[:, :inter], y[:, inter:], valid)
+        ext.grouped_gemm_into(h_q, self.w2, h_s, self.w2_scale, off, self.z)
+
+    def forward(self, x, topk_ids, topk_w, keep_trace: bool = False):
+        t = x.shape[0]
+        assert t <= self.t_max and topk_ids.shape[1] == self.topk, "batch larger than the symmetric buffers"
+        self.local_rows(x, topk_ids)
+        t0, t1 = token_range(self.rank, self.world, t)
+        self.handle.barrier(channel=0)      # every rank's z and slots are complete
+        _ext().moe_combine_exchange(self.z_ptrs, self.slot_ptrs, topk_ids, topk_w, self.out_ptrs,
+                                    self.num_experts // self.world, t0, t1, self.hidden)
+        self.handle.barrier(channel=1)      # every rank's rows have landed everywhere
+        return self.out[:t]
 
 
 def route(router_logits: torch.Tensor, topk: int):

@@ -185,6 +185,19 @@ DSV4_API int launch_gather_rows(const void* src, const int* src_row, void* dst, 
 DSV4_API int launch_moe_combine(const void* z, const int* dst_slot, const float* topk_w, void* out, int T,
                        int topk, int H, int out_f32, dsv4_stream_t stream);
 
+/* Expert-parallel combine fused with its exchange over peer memory (no reference counterpart: the
+ * reference has no collective code, README.md:104).  num_ranks (1..8) ranks each hold z (their own
+ * experts' outputs, bf16 [*,H]) and dst_slot (int32 [T*topk], -1 for experts of other ranks), the
+ * expert e living on rank e / experts_per_rank; z_ranks / slot_ranks / out_ranks are HOST arrays of
+ * num_ranks device pointers, all dereferenceable from this GPU (peer mappings).  For the tokens
+ * t0 <= t < t1 this call computes out[t,:] = sum_j topk_w[t,j] * z_rank(j)[slot(j),:] in slot order
+ * (the arithmetic of launch_moe_combine) and stores the bf16 row into every rank's out [T,H].  The
+ * caller orders it after all ranks' z are complete and makes the stores visible afterwards (e.g.
+ * symmetric-memory barriers on the stream). */
+DSV4_API int launch_moe_combine_exchange(const void* const* z_ranks, const int* const* slot_ranks,
+                       const int* topk_ids, const float* topk_w, void* const* out_ranks, int num_ranks,
+                       int experts_per_rank, int t0, int t1, int topk, int H, dsv4_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

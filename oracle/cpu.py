@@ -178,6 +178,22 @@ def moe_combine(z: torch.Tensor, dst_slot: torch.Tensor, topk_w: torch.Tensor, o
     return out
 
 
+def moe_combine_exchange(z_ranks, slot_ranks, topk_ids, topk_w, out, experts_per_rank: int, t0: int, t1: int):
+    """Rows t0..t1 of `out` (bf16 [T,H], updated in place) from the per-rank expert outputs and slot maps."""
+    g = len(z_ranks)
+    zs = [z.contiguous() for z in z_ranks]
+    ss = [s.to(torch.int32).contiguous() for s in slot_ranks]
+    zp = (ctypes.c_void_p * g)(*[z.data_ptr() for z in zs])
+    sp = (ctypes.c_void_p * g)(*[s.data_ptr() for s in ss])
+    ids = topk_ids.to(torch.int32).contiguous()
+    w = topk_w.contiguous().float()
+    assert out.is_contiguous() and out.dtype == torch.bfloat16
+    lib().oracle_moe_combine_exchange(zp, sp, _p(ids), _p(w), _p(out), ctypes.c_int(g), ctypes.c_int(experts_per_rank),
+                                      ctypes.c_int(t0), ctypes.c_int(t1), ctypes.c_int(ids.shape[1]),
+                                      ctypes.c_int(out.shape[1]))
+    return out
+
+
 def moe_topk(logits: torch.Tensor, k: int):
     """-> (ids int32 [T,k] descending, ties to the lower index; weights fp32 [T,k] softmax over the selection)."""
     logits = logits.contiguous().float()

@@ -407,6 +407,31 @@ void oracle_moe_combine(const uint16_t* z, const int32_t* dst_slot, const float*
         }
 }
 
+/* The same weighted sum when the expert outputs are spread over G ranks (expert parallelism; the
+ * reference leaves multi-GPU execution to the engine, README.md:104): expert e lives on rank
+ * e / experts_per_rank, z_ranks[r] holds rank r's rows and slot_ranks[r] its own dst_slot map
+ * (-1 for experts of other ranks).  Tokens t0 <= t < t1 only; rows outside are left untouched. */
+void oracle_moe_combine_exchange(const uint16_t* const* z_ranks, const int32_t* const* slot_ranks,
+                                 const int32_t* ids, const float* w, uint16_t* out_bf16, int G,
+                                 int experts_per_rank, int t0, int t1, int topk, int H) {
+#pragma omp parallel for schedule(static)
+    for (int t = t0; t < t1; ++t)
+        for (int h = 0; h < H; ++h) {
+            float acc = 0.0f;
+            for (int j = 0; j < topk; ++j) {
+                const int64_t pair = (int64_t)t * topk + j;
+                const int e = ids[pair];
+                if (e < 0) continue;
+                const int r = e / experts_per_rank;
+                if (r >= G) continue;
+                const int slot = slot_ranks[r][pair];
+                if (slot < 0) continue;
+                acc = fmaf(w[pair], bf16_to_f32(z_ranks[r][(int64_t)slot * H + h]), acc);
+            }
+            out_bf16[(int64_t)t * H + h] = f32_to_bf16(acc);
+        }
+}
+
 /* Router top-k (the engine's routing step, DSV4_OPERATOR_ANALYSIS.md:40): k rounds of arg-max,
  * larger logit first, ties to the lower expert index; weights = softmax over the selected logits
  * with the first (largest) one subtracted, exp in fp32 (expf), sum in selection order. */

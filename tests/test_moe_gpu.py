@@ -138,6 +138,52 @@ def test_moe_expert_slice_partials_sum_to_full():
     assert err <= 1e-2 * ref.float().abs().max().item()
 
 
+@pytest.mark.parametrize("world,t,topk", [(2, 64, 2), (4, 131, 4), (8, 40, 8), (3, 7, 12)])
+def test_moe_combine_exchange_on_one_gpu(ext, world, t, topk):
+    # the fused combine + exchange only sees pointers: with every "rank's" buffers on one GPU, each
+    # rank's call fills its token range of every output buffer, and the result must have the bits of
+    # the single-rank forward (same fma order) and of the oracle
+    from bw1000_dsv4_kernels_b200 import moe
+    h, e, inter = 512, 24, 256
+    full = wl.moe_inputs(t, h, e, inter, topk, seed=21)
+    whole = moe.W8A8MoE(full.w13.cuda(), full.w13_scale.cuda(), full.w2.cuda(), full.w2_scale.cuda(), e)
+    ref = whole.forward(full.x.cuda(), full.topk_ids.cuda(), full.topk_w.cuda())
+    ids, w = full.topk_ids.cuda(), full.topk_w.cuda()
+    zs, slots = [], []
+    for r in range(world):
+        lo, hi = moe.expert_range(r, world, e)
+        part_in = wl.moe_inputs(t, h, e, inter, topk, seed=21, expert_lo=lo, expert_hi=hi)
+        layer = moe.W8A8MoE(part_in.w13.cuda(), part_in.w13_scale.cuda(), part_in.w2.cuda(), part_in.w2_scale.cuda(),
+                            e, expert_lo=lo)
+        layer.local_partial(part_in.x.cuda(), ids, w, out_f32=True, keep_trace=True)
+        zs.append(layer.last_trace.z)
+        slots.append(layer.last_trace.dst_slot)
+    outs = [torch.full((t, h), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    for r in range(world):
+        t0, t1 = moe.token_range(r, world, t)
+        ext.moe_combine_exchange([z.data_ptr() for z in zs], [s.data_ptr() for s in slots], ids, w,
+                                 [o.data_ptr() for o in outs], e // world, t0, t1, h)
+    for r in range(world):
+        assert torch.equal(outs[r].view(torch.int16), ref.view(torch.int16)), f"rank {r}'s output buffer"
+    ref_o = torch.zeros((t, h), dtype=torch.bfloat16)
+    oracle.moe_combine_exchange([z.cpu() for z in zs], [s.cpu() for s in slots], full.topk_ids, full.topk_w, ref_o,
+                                e // world, 0, t)
+    assert torch.equal(outs[0].cpu().view(torch.int16), ref_o.view(torch.int16)), "oracle"
+
+
+def test_moe_combine_exchange_rejects_bad_arguments(ext):
+    ids = torch.zeros((4, 2), dtype=torch.int32, device="cuda")
+    w = torch.zeros((4, 2), dtype=torch.float32, device="cuda")
+    buf = torch.zeros((8, 64), dtype=torch.bfloat16, device="cuda")
+    slot = torch.zeros(8, dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError):
+        ext.moe_combine_exchange([buf.data_ptr()] * 9, [slot.data_ptr()] * 9, ids, w, [buf.data_ptr()] * 9, 1, 0, 4, 64)
+    with pytest.raises(RuntimeError):
+        ext.moe_combine_exchange([buf.data_ptr()], [slot.data_ptr()], ids, w, [buf.data_ptr()], 1, 0, 5, 64)
+    with pytest.raises(RuntimeError):
+        ext.moe_combine_exchange([0], [slot.data_ptr()], ids, w, [buf.data_ptr()], 1, 0, 4, 64)
+
+
 @pytest.mark.parametrize("t,e,k", [(4096, 256, 8), (33, 64, 6), (7, 384, 8), (5, 8, 8), (1, 256, 1)])
 def test_moe_topk_matches_oracle(cabi, ext, t, e, k):
     logits = torch.randn((t, e), generator=torch.Generator().manual_seed(t + e))

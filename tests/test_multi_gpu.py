@@ -52,6 +52,13 @@ def _worker(rank, world, port, ret):
         out_m = moe.W8A8MoE(part.w13, part.w13_scale, part.w2, part.w2_scale, e, expert_lo=lo).forward(part.x, part.topk_ids, part.topk_w)
         err = (out_m.float() - ref_m.float()).abs().max().item()
         assert err <= 1e-2 * ref_m.float().abs().max().item(), f"EP MoE off by {err}"
+        # fused combine + exchange over peer memory: the single-GPU bits on every rank, twice in a row
+        ex = moe.ExchangeW8A8MoE(part.w13, part.w13_scale, part.w2, part.w2_scale, e, rank, world, t_max=t, topk=topk,
+                                 device=dev)
+        for _ in range(2):
+            out_x = ex.forward(part.x, part.topk_ids, part.topk_w)
+            torch.cuda.synchronize()
+            assert torch.equal(out_x.view(torch.int16), ref_m.view(torch.int16)), "fused EP combine"
         ret[rank] = "ok"
     except Exception as exc:  # pragma: no cover
         import traceback

@@ -218,6 +218,34 @@ def test_moe_segments_oracle():
     assert torch.equal(dst.long()[order], torch.arange(400))
 
 
+def test_moe_combine_exchange_oracle_equals_single_rank_combine():
+    # experts spread over 1, 2 and 4 ranks (each with its own segment numbering): pulling the rows from
+    # the rank that holds them gives the bits of the single-rank combine, for any token range
+    t, e, topk, h = 37, 8, 3, 64
+    ids, w = wl.moe_routing(t, e, topk, seed=3)
+    g = torch.Generator().manual_seed(5)
+    rows = torch.randn((t * topk, h), generator=g).bfloat16()       # expert output of pair p = row p
+    _, _, dst = oracle.moe_segments(ids, e)
+    z_full = torch.zeros_like(rows)
+    z_full[dst.long()] = rows
+    ref = oracle.moe_combine(z_full, dst, w)
+    for world in (1, 2, 4):
+        per = e // world
+        zs, slots = [], []
+        for r in range(world):
+            _, _, dst_r = oracle.moe_segments(ids, per, expert_lo=r * per)
+            z_r = torch.zeros_like(rows)
+            keep = dst_r >= 0
+            z_r[dst_r[keep].long()] = rows[keep]
+            zs.append(z_r)
+            slots.append(dst_r)
+        out = torch.full((t, h), float("nan")).bfloat16()
+        for r in range(world):
+            t0, t1 = min(t, r * 10), min(t, (r + 1) * 10) if r < world - 1 else t
+            oracle.moe_combine_exchange(zs, slots, ids, w, out, per, t0, t1)
+        assert torch.equal(out.view(torch.int16), ref.view(torch.int16)), f"{world} ranks"
+
+
 # ---- frozen fixtures ----------------------------------------------------------------------
 def test_oracle_reproduces_frozen_fixtures():
     from tests.golden import make_golden
