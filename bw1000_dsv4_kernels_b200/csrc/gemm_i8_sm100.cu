@@ -882,6 +882,79 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 }
 
 
+// Split-K epilogue of the weight-streaming kernels: sums the S partial tiles ([token][128 weight
+// rows] int32, one in each peer CTA's shared memory, fixed order r = 0..S-1), applies the scales and
+// stores.  Work item = (token column c, group of four weight rows): 16-byte loads through
+// distributed shared memory, four outputs that are contiguous in C; consecutive threads take
+// consecutive row groups of one column.  Four items are in flight per thread, because one item at a
+// time would cost a full remote-load latency per item.
+template <int MAXS>
+__device__ __forceinline__ void reduce_partials_and_store(const Params& p, const uint32_t (&peer_base)[MAXS], int S,
+                                                          int cols_lo, int cols_hi, int n0, int tid, int nthreads) {
+    constexpr int U = 4;
+    const bool vec_store = p.out_i32 ? ((p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0))
+                                     : ((p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 7) == 0));
+    const int items = (cols_hi - cols_lo) * 32;
+    for (int it0 = tid; it0 < items; it0 += nthreads * U) {
+        uint4 v[U][MAXS];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int it = it0 + u * nthreads;
+            if (it < items) {
+                const uint32_t off = (uint32_t)((cols_lo + (it >> 5)) * 128 + (it & 31) * 4) * 4u;
+#pragma unroll
+                for (int r = 0; r < MAXS; ++r)
+                    if (r < S) v[u][r] = ptx::ld_shared_cluster_v4(peer_base[r] + off);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int it = it0 + u * nthreads;
+            if (it >= items) break;
+            const int c = cols_lo + (it >> 5), g = it & 31;
+            int a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+#pragma unroll
+            for (int r = 0; r < MAXS; ++r) {
+                if (r < S) {
+                    a0 += (int)v[u][r].x; a1 += (int)v[u][r].y; a2 += (int)v[u][r].z; a3 += (int)v[u][r].w;
+                }
+            }
+            const int n = n0 + g * 4;
+            if (n >= p.N) continue;
+            if (p.out_i32) {
+                int* out = static_cast<int*>(p.C) + (int64_t)c * p.ldc + n;
+                if (vec_store && n + 4 <= p.N) {
+                    *reinterpret_cast<int4*>(out) = make_int4(a0, a1, a2, a3);
+                } else {
+                    const int v4[4] = {a0, a1, a2, a3};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (n + j < p.N) out[j] = v4[j];
+                }
+            } else {
+                const float sa = __ldg(p.sa + c);
+                float sbv[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sbv[j] = (n + j < p.N) ? __ldg(p.sb + n + j) : 0.0f;
+                const uint32_t lo = pack_bf16x2_rn(__fmul_rn(__fmul_rn(__int2float_rn(a0), sa), sbv[0]),
+                                                   __fmul_rn(__fmul_rn(__int2float_rn(a1), sa), sbv[1]));
+                const uint32_t hi = pack_bf16x2_rn(__fmul_rn(__fmul_rn(__int2float_rn(a2), sa), sbv[2]),
+                                                   __fmul_rn(__fmul_rn(__int2float_rn(a3), sa), sbv[3]));
+                __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.C) + (int64_t)c * p.ldc + n;
+                if (vec_store && n + 4 <= p.N) {
+                    *reinterpret_cast<uint2*>(out) = make_uint2(lo, hi);
+                } else {
+                    const uint16_t h4[4] = {(uint16_t)(lo & 0xffffu), (uint16_t)(lo >> 16), (uint16_t)(hi & 0xffffu),
+                                            (uint16_t)(hi >> 16)};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (n + j < p.N) reinterpret_cast<uint16_t*>(out)[j] = h4[j];
+                }
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------
 // Weight-streaming kernel for few tokens (M <= 256): HBM-bound on the weight read, so the
 // operands are swapped and K is split.
@@ -1060,11 +1133,8 @@ gemm_i8_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     __syncthreads();
     ptx::cluster_sync();
 
-    if (warp >= 2) {
-        // Work item = (token column c, group of four weight rows): 16-byte loads of the S partials,
-        // four sums, four outputs that are contiguous in C.  Consecutive threads take consecutive
-        // row groups of one column.
-        const int tid = threadIdx.x - 64;
+    {
+        // all six warps take part: the producer and MMA threads are done by now
         const int cols_lo = (int)((int64_t)NTOK * split / S);
         int cols_hi = (int)((int64_t)NTOK * (split + 1) / S);
         if (cols_hi > p.M) cols_hi = p.M;
@@ -1072,53 +1142,7 @@ gemm_i8_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         uint32_t peer_base[8];
 #pragma unroll
         for (int r = 0; r < 8; ++r) peer_base[r] = ptx::map_to_cta(my_partial, r < S ? r : 0);
-        const bool vec_store = p.out_i32 ? ((p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0))
-                                         : ((p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 7) == 0));
-        const int items = (cols_hi - cols_lo) * 32;
-        for (int it = tid; it < items; it += kDrainThreads) {
-            const int c = cols_lo + (it >> 5), g = it & 31;
-            const uint32_t off = (uint32_t)(c * 128 + g * 4) * 4u;
-            int a0 = 0, a1 = 0, a2 = 0, a3 = 0;
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                if (r < S) {
-                    const uint4 v = ptx::ld_shared_cluster_v4(peer_base[r] + off);
-                    a0 += (int)v.x; a1 += (int)v.y; a2 += (int)v.z; a3 += (int)v.w;
-                }
-            }
-            const int n = n0 + g * 4;
-            if (n >= p.N) continue;
-            if (p.out_i32) {
-                int* out = static_cast<int*>(p.C) + (int64_t)c * p.ldc + n;
-                if (vec_store && n + 4 <= p.N) {
-                    *reinterpret_cast<int4*>(out) = make_int4(a0, a1, a2, a3);
-                } else {
-                    const int v4[4] = {a0, a1, a2, a3};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        if (n + j < p.N) out[j] = v4[j];
-                }
-            } else {
-                const float sa = __ldg(p.sa + c);
-                float sbv[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) sbv[j] = (n + j < p.N) ? __ldg(p.sb + n + j) : 0.0f;
-                const uint32_t lo = pack_bf16x2_rn(__fmul_rn(__fmul_rn(__int2float_rn(a0), sa), sbv[0]),
-                                                   __fmul_rn(__fmul_rn(__int2float_rn(a1), sa), sbv[1]));
-                const uint32_t hi = pack_bf16x2_rn(__fmul_rn(__fmul_rn(__int2float_rn(a2), sa), sbv[2]),
-                                                   __fmul_rn(__fmul_rn(__int2float_rn(a3), sa), sbv[3]));
-                __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.C) + (int64_t)c * p.ldc + n;
-                if (vec_store && n + 4 <= p.N) {
-                    *reinterpret_cast<uint2*>(out) = make_uint2(lo, hi);
-                } else {
-                    const uint16_t h4[4] = {(uint16_t)(lo & 0xffffu), (uint16_t)(lo >> 16), (uint16_t)(hi & 0xffffu),
-                                            (uint16_t)(hi >> 16)};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        if (n + j < p.N) reinterpret_cast<uint16_t*>(out)[j] = h4[j];
-                }
-            }
-        }
+        reduce_partials_and_store<8>(p, peer_base, S, cols_lo, cols_hi, n0, threadIdx.x, kThreads);
     }
 
     // nobody leaves while a peer may still read its shared memory
@@ -1127,6 +1151,186 @@ gemm_i8_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     if (warp == 1) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// Weight-streaming kernel for 128 < M <= 256 tokens: the same swap-AB split-K scheme on CTA pairs.
+// With 256 tokens on the MMA's N axis a single CTA re-reads the whole token block for every
+// 128-row weight tile, and that L2 -> SM traffic (not HBM) sets the time.  Here a pair of CTAs
+// owns 256 weight rows: each CTA loads its own 128 weight rows and only ITS HALF of the tokens
+// (tcgen05.mma.cta_group::2, M256 x N256), so a 128-deep K block costs each SM 32 KB instead of
+// 48 KB.  A cluster is S pairs that split K; CTA (split s, half h) has cluster rank 2s + h and
+// sums, for its share of the token columns, the partials of the S CTAs with the same h.
+// Barrier protocol of the pair as in gemm_i8_pair_kernel (full[] in the even CTA, commits arrive in
+// both CTAs).
+// ------------------------------------------------------------------------------------
+struct StreamPairSmem {
+    static constexpr int kWBytes = 128 * BK;
+    static constexpr int kXBytes = 128 * BK;   // this CTA's half of the 256 token rows
+    static constexpr int kStageBytes = kWBytes + kXBytes;
+    static constexpr int kStages = 6;
+    static constexpr int kTilesBytes = kStages * kStageBytes;
+    static constexpr int kPartialBytes = 256 * 128 * 4;
+    static_assert(kPartialBytes <= kTilesBytes, "the partial tile reuses the stage ring");
+    static constexpr int kBarOff = kTilesBytes;
+    static constexpr int kNumBars = 2 * kStages + 1;
+    static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
+    static constexpr int kAbortOff = kTmemSlotOff + 4;
+    static constexpr int kTotal = kAbortOff + 4;
+    static constexpr int kDynamic = kTotal + 1024;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_i8_stream_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                           const Params p) {
+    using L = StreamPairSmem;
+    constexpr int STAGES = L::kStages, NTOK = 256;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlotOff);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
+    int* partial = reinterpret_cast<int*>(smem);  // [NTOK][128] once the ring has drained
+
+    const uint32_t tiles_base = ptx::smem_u32(smem);
+    const uint32_t bar_base = ptx::smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    const uint32_t acc_full_bar = bar_base + 8u * (2 * STAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int csize = (int)ptx::cluster_nctarank();
+    const int crank = (int)ptx::cluster_ctarank();
+    const int S = csize >> 1, split = crank >> 1, half = crank & 1;
+    const uint32_t leader = (uint32_t)(crank & ~1);
+    const uint16_t pair_mask = (uint16_t)(0x3u << leader);
+    const int nt = blockIdx.x / csize;
+    const int n0 = nt * 256 + half * 128;         // this CTA's weight rows
+    constexpr uint32_t kTmemCols = NTOK;
+
+    const int k_blocks = (p.K + BK - 1) / BK;
+    const int kb0 = (int)((int64_t)k_blocks * split / S), kb1 = (int)((int64_t)k_blocks * (split + 1) / S);
+    bool ok = true;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        ptx::mbar_init(acc_full_bar, 1);
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+        ptx::prefetch_tensormap(&tmW);
+        ptx::prefetch_tensormap(&tmX);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();  // the peers' barriers exist before anything arrives on them
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (ptx::elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u) || *abort_flag) {
+                    report_wait_failure(kWaitEmptyStage);
+                    *abort_flag = 1;
+                    break;
+                }
+                const uint32_t w_dst = tiles_base + stage * L::kStageBytes;
+                const uint32_t leader_full = ptx::map_to_cta(full_bar(stage), leader);
+                if (half == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * L::kStageBytes);
+                ptx::tma_load_2d_pair(w_dst, &tmW, kb * BK, n0, leader_full);
+                ptx::tma_load_2d_pair(w_dst + L::kWBytes, &tmX, kb * BK, half * 128, leader_full);
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        if (half == 0 && ptx::elect_one()) {
+            constexpr uint32_t idesc = ptx::idesc_i8(256, NTOK);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool issued_all = true;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                if (!ptx::mbar_wait_bounded(full_bar(stage), phase) || *abort_flag) {
+                    report_wait_failure(kWaitFullStage);
+                    *abort_flag = 1;
+                    issued_all = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t w_src = tiles_base + stage * L::kStageBytes;
+                const uint64_t adesc = ptx::smem_desc_k_sw128(w_src);
+                const uint64_t bdesc = ptx::smem_desc_k_sw128(w_src + L::kWBytes);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    ptx::mma_i8_ss_pair(tmem_base, adesc + 2u * k, bdesc + 2u * k, idesc, (kb > kb0 || k != 0) ? 1u : 0u);
+                ptx::tc_commit_pair(empty_bar(stage), pair_mask);  // frees the stage in both CTAs
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+            if (issued_all) ptx::tc_commit_pair(acc_full_bar, pair_mask);
+        }
+    } else {
+        // drain warps of both CTAs: accumulator of this CTA's 128 weight rows -> shared partial
+        const int quarter = warp & 3;
+        const int wrow = quarter * 32 + lane;
+        if (kb1 > kb0) {
+            if (!ptx::mbar_wait_bounded(acc_full_bar, 0) || *abort_flag) {
+                report_wait_failure(kWaitAccFull);
+                *abort_flag = 1;
+                ok = false;
+            }
+        }
+        ptx::tc_fence_after_sync();
+        __syncwarp();
+        if (ok) {
+            const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+            for (int cc = 0; cc < NTOK / 32; ++cc) {
+                uint32_t r[32];
+                if (kb1 > kb0) {
+                    ptx::tmem_ld_32x32b_x32(t_lane + cc * 32, r);
+                    ptx::tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = 0;  // a pair without K blocks contributes zero
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) partial[(cc * 32 + j) * 128 + wrow] = (int)r[j];
+            }
+        }
+    }
+
+    // every CTA's partial is complete and visible to the cluster
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();
+
+    {
+        const int cols_lo = (int)((int64_t)NTOK * split / S);
+        int cols_hi = (int)((int64_t)NTOK * (split + 1) / S);
+        if (cols_hi > p.M) cols_hi = p.M;
+        const uint32_t my_partial = ptx::smem_u32(partial);
+        uint32_t peer_base[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) peer_base[r] = ptx::map_to_cta(my_partial, (uint32_t)(2 * (r < S ? r : 0) + half));
+        reduce_partials_and_store<4>(p, peer_base, S, cols_lo, cols_hi, n0, threadIdx.x, kThreads);
+    }
+
+    // nobody leaves while a peer may still read its shared memory
+    __syncthreads();
+    ptx::cluster_sync();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
     }
 }
 
@@ -1241,6 +1445,65 @@ int launch_stream_variant(const CUtensorMap& tmW, const CUtensorMap& tmX, const 
     return check_launch("w8a8_gemm (weight streaming)");
 }
 
+// How many clusters of 2*splits CTAs of the pair streaming kernel the device can run at once (one
+// CTA per SM, a cluster inside one GPC); asked once per device and cluster size.
+int stream_pair_active_clusters(int splits) {
+    static int cached[64][5] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || splits < 1 || splits > 4) return 0;
+    if (cached[dev][splits] == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(2 * splits * 64), 1, 1);
+        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = StreamPairSmem::kDynamic;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)(2 * splits);
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_i8_stream_pair_kernel, &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            n = -1;
+        }
+        cached[dev][splits] = n > 0 ? n : -1;
+    }
+    return cached[dev][splits] > 0 ? cached[dev][splits] : 0;
+}
+
+int launch_stream_pair(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, int n_tiles, int splits,
+                       cudaStream_t st) {
+    using L = StreamPairSmem;
+    static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
+    static bool opted_in[64] = {};
+    if (!opt_in_shared_memory(gemm_i8_stream_pair_kernel, L::kDynamic, opted_in))
+        return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: cannot raise the dynamic shared memory limit");
+    // a cluster must fit into one GPC: take the widest K split whose clusters all run in one wave
+    while (splits > 1 && stream_pair_active_clusters(splits) < n_tiles) --splits;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(n_tiles * 2 * splits), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = L::kDynamic;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)(2 * splits);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_i8_stream_pair_kernel, tmW, tmX, p);
+    if (err != cudaSuccess) {
+        cudaGetLastError();  // clear the sticky launch error
+        static thread_local char msg[160];
+        snprintf(msg, sizeof msg, "w8a8_gemm (weight streaming, CTA pairs): %s", cudaGetErrorString(err));
+        return fail(DSV4_ERR_LAUNCH, msg);
+    }
+    return check_launch("w8a8_gemm (weight streaming, CTA pairs)");
+}
+
 template <int STAGES>
 int launch_gs_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, int max_tiles, cudaStream_t st) {
     using L = Smem<GSN, STAGES>;
@@ -1348,8 +1611,21 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
     }
     // Few tokens: stream the weight once, tokens on the MMA's N axis, K split over a cluster
     if (!grouped && a.M <= 256 && a.npeers == 0) {
-        const int n_tiles = (a.N + 127) / 128;
         const int k_blocks = (a.K + BK - 1) / BK;
+        if (a.M > 128 && a.N >= 256) {
+            // 129..256 tokens: CTA pairs halve the token traffic per SM
+            const int pair_tiles = (a.N + 255) / 256;
+            int psplits = sms / (2 * pair_tiles);
+            if (psplits > 4) psplits = 4;
+            if (psplits > k_blocks) psplits = k_blocks;
+            if (psplits < 1) psplits = 1;
+            int rc5 = make_tile_map(&tmA, a.B, b_rows, (uint64_t)a.K, 128);   // weights
+            if (rc5) return rc5;
+            rc5 = make_tile_map(&tmB, a.A, (uint64_t)a.M, (uint64_t)a.K, 128);  // this CTA's half of the tokens
+            if (rc5) return rc5;
+            return launch_stream_pair(tmA, tmB, p, pair_tiles, psplits, st);
+        }
+        const int n_tiles = (a.N + 127) / 128;
         int splits = sms / n_tiles;
         if (splits > 8) splits = 8;
         if (splits > k_blocks) splits = k_blocks;

@@ -44,6 +44,9 @@ SHAPES = [
     (5, 72, 16),         # smallest K
     (300, 1000, 4096),
     (64, 7168, 18432),   # down projection, long K: |acc| exceeds 2^24
+    (200, 1000, 1040),   # 129..256 tokens: weight streaming on CTA pairs, ragged N and K
+    (129, 256, 16),      # the same with a single K block (no split)
+    (256, 1160, 400),    # last pair tile half empty
 ]
 
 
