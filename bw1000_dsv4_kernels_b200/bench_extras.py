@@ -86,6 +86,33 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launch
         del xs, rs, qs
     res["add_rmsnorm_quant K=7168"] = quant_sec
     res["w8a8_gemm N=4096 K=7168"] = gemm_sec
+    # the dependent chain at decode sizes, strictly serialised and with the GEMM allowed to overlap
+    # the quantiser before it (set-up and weight loads start early; see set_overlap_previous_kernel)
+    chain_sec = {}
+    for m in (1, 16, 64, 256):
+        n = 6
+        xs = [wl.randn_bf16((m, K), device=dev, seed=i) for i in range(n)]
+        rs = [wl.randn_bf16((m, K), device=dev, seed=100 + i) for i in range(n)]
+
+        def step(i):
+            q, s = ext.add_rmsnorm_quant(rs[i % n], xs[i % n], gamma, 1e-6)
+            return ext.w8a8_scaled_gemm(q, w_sets[i % NW], s, w_scale)
+
+        def lone(i):
+            return ext.w8a8_scaled_gemm(qs1[0], w_sets[i % NW], qs1[1], w_scale)
+
+        qs1 = ext.add_rmsnorm_quant(rs[0].clone(), xs[0], gamma, 1e-6)
+        us_serial = 1e3 * time_launches_graph(step)
+        try:
+            ext.set_overlap_previous_kernel(True)
+            us_overlap = 1e3 * time_launches_graph(step)
+            us_gemm_overlap = 1e3 * time_launches_graph(lone)
+        finally:
+            ext.set_overlap_previous_kernel(False)
+        chain_sec[f"M={m}"] = {"us_per_step": round(us_serial, 3), "us_per_step_overlap": round(us_overlap, 3),
+                               "us_gemm_back_to_back_overlap": round(us_gemm_overlap, 3)}
+        del xs, rs, qs1
+    res["chain add_rmsnorm_quant->w8a8_gemm N=4096 K=7168 (decode sizes)"] = chain_sec
     # cuBLASLt through torch._int_mm on the same operands, int32 output, no scale epilogue: a
     # library reference point only, not part of the product path
     try:

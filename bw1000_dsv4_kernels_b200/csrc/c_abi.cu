@@ -44,6 +44,8 @@ using namespace w8a8;
 extern "C" {
 
 int dsv4_abi_version(void) { return DSV4_ABI_VERSION; }
+void dsv4_set_overlap_previous_kernel(int enable) { set_overlap_previous_kernel(enable); }
+int dsv4_get_overlap_previous_kernel(void) { return overlap_previous_kernel(); }
 
 const char* dsv4_last_error(void) { return g_last_error; }
 

@@ -22,6 +22,7 @@
 // hip_kernels/w8a8_gemm_intmm_fused.hip:34: (float(acc) * sa[row]) * sb[col] -> bf16.
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <atomic>
 #include <cuda_bf16.h>
 #include <cstdint>
 #include <cstdio>
@@ -35,6 +36,12 @@ namespace w8a8 {
 
 // Sticky per-device status word written by kernels whose bounded waits ran out.
 __device__ int g_device_status = 0;
+
+// Process-wide option: launch the weight-streaming GEMMs (M <= 256) so that they may overlap the
+// kernel before them on the stream (programmatic dependent launch).  Off by default.
+static std::atomic<int> g_overlap_previous{0};
+void set_overlap_previous_kernel(int on) { g_overlap_previous.store(on ? 1 : 0, std::memory_order_relaxed); }
+int overlap_previous_kernel() { return g_overlap_previous.load(std::memory_order_relaxed); }
 
 namespace {
 
@@ -1005,6 +1012,7 @@ gemm_i8_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     const uint32_t acc_full_bar = bar_base + 8u * (2 * STAGES);
 
+    ptx::grid_launch_dependents();  // a kernel launched to overlap this one may start its set-up and weight loads
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int S = (int)ptx::cluster_nctarank();
     const int split = (int)ptx::cluster_ctarank();
@@ -1029,12 +1037,16 @@ gemm_i8_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async_smem();
+        // The weight does not depend on the kernel that runs before this one: its loads start at once.
+        // The tokens do: their loads come after the dependency wait (which returns immediately unless
+        // this kernel was launched to overlap its predecessor).
         for (int i = 0; i < prologue; ++i) {
-            const uint32_t w_dst = tiles_base + i * L::kStageBytes;
             ptx::mbar_arrive_expect_tx(full_bar(i), L::kStageBytes);
-            ptx::tma_load_2d(w_dst, &tmW, (kb0 + i) * BK, n0, full_bar(i));
-            ptx::tma_load_2d(w_dst + L::kWBytes, &tmX, (kb0 + i) * BK, 0, full_bar(i));
+            ptx::tma_load_2d(tiles_base + i * L::kStageBytes, &tmW, (kb0 + i) * BK, n0, full_bar(i));
         }
+        ptx::grid_dependency_wait();
+        for (int i = 0; i < prologue; ++i)
+            ptx::tma_load_2d(tiles_base + i * L::kStageBytes + L::kWBytes, &tmX, (kb0 + i) * BK, 0, full_bar(i));
     }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
@@ -1132,6 +1144,7 @@ gemm_i8_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::cluster_sync();
+    ptx::grid_dependency_wait();     // before this thread reads activation scales or writes C
 
     {
         // all six warps take part: the producer and MMA threads are done by now
@@ -1199,6 +1212,7 @@ gemm_i8_stream_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     const uint32_t acc_full_bar = bar_base + 8u * (2 * STAGES);
 
+    ptx::grid_launch_dependents();  // a kernel launched to overlap this one may start its set-up and weight loads
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int csize = (int)ptx::cluster_nctarank();
     const int crank = (int)ptx::cluster_ctarank();
@@ -1237,9 +1251,21 @@ gemm_i8_stream_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
 
     if (warp == 0) {
         if (ptx::elect_one()) {
-            int stage = 0;
-            uint32_t phase = 0;
-            for (int kb = kb0; kb < kb1; ++kb) {
+            // first ring-full: the stages are free; the weight loads go out before the dependency wait
+            // (the weight does not depend on the preceding kernel), the token loads after it
+            const int prologue = (kb1 - kb0) < STAGES ? (kb1 - kb0) : STAGES;
+            for (int i = 0; i < prologue; ++i) {
+                const uint32_t leader_full = ptx::map_to_cta(full_bar(i), leader);
+                if (half == 0) ptx::mbar_arrive_expect_tx(full_bar(i), 2 * L::kStageBytes);
+                ptx::tma_load_2d_pair(tiles_base + i * L::kStageBytes, &tmW, (kb0 + i) * BK, n0, leader_full);
+            }
+            ptx::grid_dependency_wait();
+            for (int i = 0; i < prologue; ++i)
+                ptx::tma_load_2d_pair(tiles_base + i * L::kStageBytes + L::kWBytes, &tmX, (kb0 + i) * BK, half * 128,
+                                      ptx::map_to_cta(full_bar(i), leader));
+            int stage = prologue == STAGES ? 0 : prologue;
+            uint32_t phase = prologue == STAGES ? 1u : 0u;
+            for (int kb = kb0 + prologue; kb < kb1; ++kb) {
                 if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u) || *abort_flag) {
                     report_wait_failure(kWaitEmptyStage);
                     *abort_flag = 1;
@@ -1313,6 +1339,7 @@ gemm_i8_stream_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::cluster_sync();
+    ptx::grid_dependency_wait();     // before this thread reads activation scales or writes C
 
     {
         const int cols_lo = (int)((int64_t)NTOK * split / S);
@@ -1428,13 +1455,15 @@ int launch_stream_variant(const CUtensorMap& tmW, const CUtensorMap& tmX, const 
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = L::kDynamic;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = (unsigned)splits;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = overlap_previous_kernel() ? 2 : 1;
     const cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_i8_stream_kernel<NTOK>, tmW, tmX, p);
     if (err != cudaSuccess) {
         cudaGetLastError();  // clear the sticky launch error
@@ -1487,13 +1516,15 @@ int launch_stream_pair(const CUtensorMap& tmW, const CUtensorMap& tmX, const Par
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = L::kDynamic;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = (unsigned)(2 * splits);
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = overlap_previous_kernel() ? 2 : 1;
     const cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_i8_stream_pair_kernel, tmW, tmX, p);
     if (err != cudaSuccess) {
         cudaGetLastError();  // clear the sticky launch error

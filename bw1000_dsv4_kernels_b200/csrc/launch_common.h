@@ -51,6 +51,8 @@ int gather_rows(const void* src, const int* src_row, void* dst, int R, int row_b
 int moe_topk(const float* logits, int T, int E, int k, int* ids, float* weights, cudaStream_t st);
 int moe_combine(const void* z, const int* dst_slot, const float* w, void* out, int T, int topk, int H,
                 int out_f32, cudaStream_t st);
+void set_overlap_previous_kernel(int on);
+int overlap_previous_kernel();
 int moe_combine_exchange(const void* const* z_ranks, const int* const* slot_ranks, const int* topk_ids,
                          const float* topk_w, void* const* out_ranks, int G, int experts_per_rank, int t0, int t1,
                          int topk, int H, cudaStream_t st);

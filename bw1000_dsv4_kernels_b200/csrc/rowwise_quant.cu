@@ -89,6 +89,7 @@ __global__ void __launch_bounds__(1024) ptq_vec_kernel(const __nv_bfloat16* __re
                                                        int8_t* __restrict__ q,
                                                        float* __restrict__ s, int M, int K,
                                                        int64_t ldx) {
+    ptx::grid_launch_dependents();  // a GEMM launched to overlap this kernel may start its set-up and weight loads
     __shared__ float red[32];
     const int V = K >> 3, T = blockDim.x, tid = threadIdx.x;
     for (int row = blockIdx.x; row < M; row += gridDim.x) {
@@ -126,6 +127,7 @@ __global__ void __launch_bounds__(256) ptq_generic_kernel(const __nv_bfloat16* _
                                                           int8_t* __restrict__ q,
                                                           float* __restrict__ s, int M, int K,
                                                           int64_t ldx) {
+    ptx::grid_launch_dependents();  // a GEMM launched to overlap this kernel may start its set-up and weight loads
     __shared__ float red[32];
     for (int row = blockIdx.x; row < M; row += gridDim.x) {
         const __nv_bfloat16* xr = x + (int64_t)row * ldx;
@@ -222,6 +224,7 @@ __global__ void __launch_bounds__(kSumLanes) add_rmsnorm_quant_vec_kernel(
     __nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ x,
     const __nv_bfloat16* __restrict__ w, int8_t* __restrict__ q, float* __restrict__ s, int M,
     int K, float eps) {
+    ptx::grid_launch_dependents();  // a GEMM launched to overlap this kernel may start its set-up and weight loads
     __shared__ float red_sum[8];
     __shared__ float red_max[32];
     const int V = K >> 3, tid = threadIdx.x;
@@ -303,6 +306,7 @@ __global__ void __launch_bounds__(kSumLanes) add_rmsnorm_quant_generic_kernel(
     __nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ x,
     const __nv_bfloat16* __restrict__ w, int8_t* __restrict__ q, float* __restrict__ s, int M,
     int K, float eps) {
+    ptx::grid_launch_dependents();  // a GEMM launched to overlap this kernel may start its set-up and weight loads
     __shared__ float red_sum[8];
     __shared__ float red_max[32];
     for (int row = blockIdx.x; row < M; row += gridDim.x) {
@@ -408,6 +412,7 @@ __global__ void __launch_bounds__(T, MINB) silu_mul_quant_vec_kernel(
     const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
     const int* __restrict__ mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
     float* __restrict__ s, int M, int N, int64_t ldg, int64_t ldu) {
+    ptx::grid_launch_dependents();  // a GEMM launched to overlap this kernel may start its set-up and weight loads
     extern __shared__ float4 h_row4[];  // N floats, 16-byte aligned
     __shared__ float red[32];
     const int V = N >> 3, tid = threadIdx.x;
@@ -471,6 +476,7 @@ __global__ void __launch_bounds__(T, MINB) silu_mul_quant_table_kernel(
     const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
     const int* __restrict__ mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
     float* __restrict__ s, int M, int N, int64_t ldg, int64_t ldu) {
+    ptx::grid_launch_dependents();  // a GEMM launched to overlap this kernel may start its set-up and weight loads
     extern __shared__ float4 h_row4[];
     __shared__ float red[32];
     float* tab = reinterpret_cast<float*>(h_row4) + N;
@@ -554,6 +560,7 @@ __global__ void __launch_bounds__(1024, 1) silu_mul_quant_async_kernel(
     const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
     const int* __restrict__ mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
     float* __restrict__ s, int M, int N, int64_t ldg, int64_t ldu) {
+    ptx::grid_launch_dependents();  // a GEMM launched to overlap this kernel may start its set-up and weight loads
     constexpr int GROUP = 512, GT = GROUP / RPB, WPG = GT / 32;  // threads per group / per row, warps per row
     extern __shared__ uint4 smem4[];
     __shared__ float red[2][2][RPB][WPG];  // [group][parity][row][warp]
@@ -676,6 +683,7 @@ __global__ void __launch_bounds__(256) silu_mul_quant_generic_kernel(
     const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
     const int* __restrict__ mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
     float* __restrict__ s, int M, int N, int64_t ldg, int64_t ldu) {
+    ptx::grid_launch_dependents();  // a GEMM launched to overlap this kernel may start its set-up and weight loads
     __shared__ float red[32];
     if (valid_rows != nullptr) M = min(M, __ldg(valid_rows));
     for (int row = blockIdx.x; row < M; row += gridDim.x) {

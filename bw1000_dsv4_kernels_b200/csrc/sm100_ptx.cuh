@@ -251,6 +251,12 @@ __device__ __forceinline__ uint4 ld_shared_cluster_v4(uint32_t cluster_addr) {
                  : "memory");
     return v;
 }
+// Programmatic dependent launch.  wait: returns once every kernel this one depends on has completed
+// and its memory is visible (immediately if the kernel was launched without the attribute).
+// launch_dependents: lets a dependent kernel that was launched with the attribute start its
+// pre-wait part now.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ uint32_t cluster_nctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));

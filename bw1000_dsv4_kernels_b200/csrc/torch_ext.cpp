@@ -545,4 +545,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("w8a8_gemm_allgather_stream", &w8a8_gemm_allgather_stream);
     m.def("device_status", &device_status);
     m.def("abi_version", [] { return dsv4_abi_version(); });
+    m.def("set_overlap_previous_kernel", [](bool on) { dsv4_set_overlap_previous_kernel(on ? 1 : 0); },
+          "GEMMs with M <= 256 may start (set-up, weight loads) while the previous kernel on the stream still runs");
+    m.def("get_overlap_previous_kernel", [] { return dsv4_get_overlap_previous_kernel() != 0; });
 }

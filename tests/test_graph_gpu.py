@@ -52,3 +52,50 @@ def test_stream_variant_under_capture_matches_patch_wrapper(ext):
     torch.cuda.synchronize()
     q_ref, s_ref = oracle.per_token_quant_int8(x2)
     assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref)
+
+
+@pytest.mark.parametrize("m", [1, 16, 64, 200, 256])
+def test_overlap_with_previous_kernel_gives_the_same_bits(ext, m):
+    # with the option on, the GEMM for M <= 256 starts (set-up, weight loads) while the quantiser
+    # before it is still running and waits for it only before it touches activations or output:
+    # a chain of dependent launches, eagerly and from a CUDA graph, must give the bits of the
+    # fully serialised run, also when every step reuses the same buffers
+    k, n = 2048, 1024
+    steps = [wl.norm_gemm_inputs(m, k=k, n=n, seed=30 + i) for i in range(4)]
+    gamma, w, ws = steps[0].gamma.cuda(), steps[0].w.cuda(), steps[0].w_scale.cuda()
+    x, res = torch.empty_like(steps[0].x, device="cuda"), torch.empty_like(steps[0].res, device="cuda")
+    keep = torch.empty((len(steps), m, n), dtype=torch.bfloat16, device="cuda")
+
+    def run_eager():
+        for i, st in enumerate(steps):
+            x.copy_(st.x, non_blocking=True)
+            res.copy_(st.res, non_blocking=True)
+            q, s = ext.add_rmsnorm_quant(res, x, gamma, 1e-6)
+            keep[i].copy_(ext.w8a8_scaled_gemm(q, w, s, ws))
+        torch.cuda.synchronize()
+        return keep.clone()
+
+    assert not ext.get_overlap_previous_kernel()
+    ref = run_eager()
+    try:
+        ext.set_overlap_previous_kernel(True)
+        assert ext.get_overlap_previous_kernel()
+        out = run_eager()
+        assert torch.equal(out.view(torch.int16), ref.view(torch.int16)), "eager launches"
+        xs = torch.stack([st.x for st in steps]).cuda()
+        rs = torch.stack([st.res for st in steps]).cuda()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(len(steps)):
+                q, s = ext.add_rmsnorm_quant(rs[i], xs[i], gamma, 1e-6)
+                y = ext.w8a8_scaled_gemm(q, w, s, ws)
+                keep[i].copy_(y)
+        for _ in range(2):
+            rs.copy_(torch.stack([st.res for st in steps]))
+            keep.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(keep.view(torch.int16), ref.view(torch.int16)), "graph replay"
+    finally:
+        ext.set_overlap_previous_kernel(False)
+    assert ext.device_status() == 0
