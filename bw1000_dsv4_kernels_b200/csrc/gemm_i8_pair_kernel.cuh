@@ -64,6 +64,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
     auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
 
+    ptx::grid_launch_dependents();  // a kernel launched to overlap this one may start its set-up and weight loads
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = ptx::cluster_ctarank();
     constexpr uint32_t kTmemCols = 512;
@@ -102,27 +103,57 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
         if (ptx::elect_one()) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int t = pair; t < total && ok; t += npairs) {
-                const int mt = t % tiles_m, nt = t / tiles_m;
-                const int a_row0 = mt * 256 + (int)rank * 128;
-                const int b_row0 = nt * PBN + (int)rank * 128;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+            // The first ring-full needs no free-stage wait; its B (weight) tiles are requested before the
+            // dependency wait and its A tiles after it, so that a launch that overlaps the preceding
+            // kernel (see set_overlap_previous_kernel) streams weights while that kernel still runs.
+            // (t, kb) walks this pair's tiles and their K blocks.
+            struct Cursor {
+                int t, kb;
+            };
+            auto advance = [&](Cursor& c) {
+                if (++c.kb == k_blocks) {
+                    c.kb = 0;
+                    c.t += npairs;
+                }
+            };
+            Cursor c0{pair, 0};
+            int first = 0;
+            for (Cursor c = c0; first < STAGES && c.t < total; ++first, advance(c)) {
+                const int b_row0 = (c.t / tiles_m) * PBN + (int)rank * 128;
+                if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(first), 2 * L::kStageBytes);
+                ptx::tma_load_2d_pair(tiles_base + first * L::kStageBytes + L::kABytes, &tmB, c.kb * BK, b_row0,
+                                      ptx::map_to_cta(full_bar(first), 0));
+            }
+            ptx::grid_dependency_wait();
+            Cursor c = c0;
+            for (int i = 0; i < first; ++i, advance(c)) {
+                const int a_row0 = (c.t % tiles_m) * 256 + (int)rank * 128;
+                ptx::tma_load_2d_pair(tiles_base + i * L::kStageBytes, &tmA, c.kb * BK, a_row0,
+                                      ptx::map_to_cta(full_bar(i), 0));
+            }
+            int stage = first == STAGES ? 0 : first;
+            uint32_t phase = first == STAGES ? 1u : 0u;
+            while (c.t < total) {
+                const int a_row0 = (c.t % tiles_m) * 256 + (int)rank * 128;
+                const int b_row0 = (c.t / tiles_m) * PBN + (int)rank * 128;
+                for (; c.kb < k_blocks; ++c.kb) {
                     if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u) || *abort_flag) {
                         report_wait_failure(kWaitEmptyStage);
                         *abort_flag = 1;
-                        ok = false;
+                        c.t = total;  // leave both loops
                         break;
                     }
                     const uint32_t a_dst = tiles_base + stage * L::kStageBytes;
                     const uint32_t b_dst = a_dst + L::kABytes;
                     const uint32_t leader_full = ptx::map_to_cta(full_bar(stage), 0);
                     if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * L::kStageBytes);
-                    ptx::tma_load_2d_pair(a_dst, &tmA, kb * BK, a_row0, leader_full);
-                    ptx::tma_load_2d_pair(b_dst, &tmB, kb * BK, b_row0, leader_full);
+                    ptx::tma_load_2d_pair(a_dst, &tmA, c.kb * BK, a_row0, leader_full);
+                    ptx::tma_load_2d_pair(b_dst, &tmB, c.kb * BK, b_row0, leader_full);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (c.t < total) {
+                    c.kb = 0;
+                    c.t += npairs;
                 }
             }
         }
@@ -169,6 +200,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
     } else {
         // ---------------- drain warps (both CTAs) ----------------
+        ptx::grid_dependency_wait();  // before reading activation scales or writing C
         const int quarter = warp & 3;
         float* sbs = sb_tile + (warp - 2) * PBN;
         int acc = 0;

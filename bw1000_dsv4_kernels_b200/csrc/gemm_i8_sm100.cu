@@ -39,8 +39,9 @@
 
 namespace w8a8 {
 
-// Process-wide option: launch the weight-streaming GEMMs (M <= 256) so that they may overlap the
-// kernel before them on the stream (programmatic dependent launch).  Off by default.
+// Process-wide option: launch the dense GEMMs (weight-streaming kernels for M <= 256, CTA-pair kernel
+// above) so that they may overlap the kernel before them on the stream (programmatic dependent
+// launch).  Off by default.
 static std::atomic<int> g_overlap_previous{0};
 void set_overlap_previous_kernel(int on) { g_overlap_previous.store(on ? 1 : 0, std::memory_order_relaxed); }
 int overlap_previous_kernel() { return g_overlap_previous.load(std::memory_order_relaxed); }
@@ -263,7 +264,27 @@ int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Pa
     int pairs = sm_count() / 2;
     if (pairs <= 0) return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: no CUDA device");
     if (tiles < pairs) pairs = tiles;
-    gemm_i8_pair_kernel<STAGES, TMA_STORE><<<2 * pairs, kThreads, L::kDynamic, st>>>(tmA, tmB, p, smaps);
+    if (!overlap_previous_kernel()) {
+        gemm_i8_pair_kernel<STAGES, TMA_STORE><<<2 * pairs, kThreads, L::kDynamic, st>>>(tmA, tmB, p, smaps);
+        return check_launch("w8a8_gemm");
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = L::kDynamic;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_i8_pair_kernel<STAGES, TMA_STORE>, tmA, tmB, p, smaps);
+    if (err != cudaSuccess) {
+        cudaGetLastError();  // clear the sticky launch error
+        static thread_local char msg[160];
+        snprintf(msg, sizeof msg, "w8a8_gemm (CTA pairs): %s", cudaGetErrorString(err));
+        return fail(DSV4_ERR_LAUNCH, msg);
+    }
     return check_launch("w8a8_gemm");
 }
 

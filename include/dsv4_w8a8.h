@@ -50,8 +50,8 @@ DSV4_API const char* dsv4_last_error(void);
  * Intended for tests and post-mortems; the launch path never calls it. */
 DSV4_API int dsv4_device_status(dsv4_stream_t stream, int* status_out);
 
-/* Process-wide option, off by default (no reference counterpart).  When enabled, the GEMM
- * launchers for M <= 256 (weight-streaming kernels) start with programmatic dependent launch: the
+/* Process-wide option, off by default (no reference counterpart).  When enabled, the dense GEMM
+ * launchers (not the grouped ones) start with programmatic dependent launch: the
  * kernel may begin while the kernel before it on the stream is still running, sets itself up and
  * starts streaming the WEIGHT, and waits for that kernel to complete only before it reads the
  * activations and their scales or writes its output.  The row kernels of this library let such a

@@ -99,3 +99,31 @@ def test_overlap_with_previous_kernel_gives_the_same_bits(ext, m):
     finally:
         ext.set_overlap_previous_kernel(False)
     assert ext.device_status() == 0
+
+
+def test_overlap_option_on_the_cta_pair_gemm(ext):
+    # M large enough for the CTA-pair kernel: the same contract (weight tiles before the dependency wait,
+    # activation tiles and the epilogue after it), same bits as the serialised run
+    m, k, n = 1024, 1024, 2304
+    steps = [wl.norm_gemm_inputs(m, k=k, n=n, seed=50 + i) for i in range(3)]
+    gamma, w, ws = steps[0].gamma.cuda(), steps[0].w.cuda(), steps[0].w_scale.cuda()
+    xs = torch.stack([st.x for st in steps]).cuda()
+    rs0 = torch.stack([st.res for st in steps]).cuda()
+
+    def run():
+        rs = rs0.clone()
+        outs = []
+        for i in range(len(steps)):
+            q, s = ext.add_rmsnorm_quant(rs[i], xs[i], gamma, 1e-6)
+            outs.append(ext.w8a8_scaled_gemm(q, w, s, ws))
+        torch.cuda.synchronize()
+        return torch.stack(outs)
+
+    ref = run()
+    try:
+        ext.set_overlap_previous_kernel(True)
+        out = run()
+    finally:
+        ext.set_overlap_previous_kernel(False)
+    assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
+    assert ext.device_status() == 0
