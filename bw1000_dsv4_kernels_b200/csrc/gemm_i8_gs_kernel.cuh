@@ -148,6 +148,9 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             __syncwarp();
             const int row = c.a_row0 + quarter * 32 + lane;
             const bool row_ok = row < c.row_end;
+            // A warp whose 32 rows all lie past the end of the segment (the mostly empty last tile of
+            // an expert) only keeps the buffer hand-over going: no tensor-memory loads, no arithmetic.
+            const bool warp_has_rows = c.a_row0 + quarter * 32 < c.row_end;
             const float* sa_row = p.sa + (int64_t)(row_ok ? row : 0) * p.sa_groups;
             // y as float2 lanes: the fold below runs on packed f32x2 instructions.  float(acc) is
             // formed without a conversion instruction (those issue at a quarter of the FMA rate):
@@ -175,6 +178,11 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 }
                 ptx::tc_fence_after_sync();
                 __syncwarp();  // tcgen05.ld is warp-collective
+                if (!warp_has_rows) {
+                    ptx::tc_fence_before_sync();
+                    if (lane == 0) ptx::mbar_arrive(blk_empty_bar(b));
+                    continue;
+                }
                 const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + b * GSN + half * HC;
                 const float2 sg2 = splat2(sg), unbias = splat2(-12582912.0f);
 #pragma unroll
