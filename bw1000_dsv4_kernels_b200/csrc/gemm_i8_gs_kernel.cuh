@@ -185,23 +185,34 @@ gemm_i8_gs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 }
                 const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + b * GSN + half * HC;
                 const float2 sg2 = splat2(sg), unbias = splat2(-12582912.0f);
+                // eight columns per tcgen05.ld, two loads deep: the load of the next eight columns is in
+                // flight while the current eight are folded into y
+                uint32_t ra[8], rb[8];
+                auto fold = [&](const uint32_t (&r)[8], int c8) {
 #pragma unroll
-                for (int cc = 0; cc < HC / 16; ++cc) {
-                    uint32_t r0[16];
-                    ptx::tmem_ld_32x32b_x16(t_lane + cc * 16, r0);
+                    for (int j = 0; j < 4; ++j) {
+                        float2 f = make_float2(__int_as_float((int)r[2 * j] + 0x4B400000),
+                                               __int_as_float((int)r[2 * j + 1] + 0x4B400000));
+                        y2[c8 * 4 + j] = __ffma2_rn(__fadd2_rn(f, unbias), sg2, y2[c8 * 4 + j]);
+                    }
+                };
+                ptx::tmem_ld_32x32b_x8(t_lane, ra);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int c8 = 0; c8 < HC / 8; c8 += 2) {
+                    ptx::tmem_ld_32x32b_x8(t_lane + (c8 + 1) * 8, rb);
+                    fold(ra, c8);
                     ptx::tmem_ld_wait();
-                    if (cc == HC / 16 - 1) {
+                    if (c8 + 2 < HC / 8) {
+                        ptx::tmem_ld_32x32b_x8(t_lane + (c8 + 2) * 8, ra);
+                    } else {
                         // the last columns are in registers: the accumulator can be overwritten
                         ptx::tc_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(blk_empty_bar(b));
                     }
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        float2 f = make_float2(__int_as_float((int)r0[2 * j] + 0x4B400000),
-                                               __int_as_float((int)r0[2 * j + 1] + 0x4B400000));
-                        y2[cc * 8 + j] = __ffma2_rn(__fadd2_rn(f, unbias), sg2, y2[cc * 8 + j]);
-                    }
+                    fold(rb, c8 + 1);
+                    if (c8 + 2 < HC / 8) ptx::tmem_ld_wait();
                 }
             }
             if (!ok) break;
