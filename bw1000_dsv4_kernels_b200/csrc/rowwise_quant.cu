@@ -467,10 +467,10 @@ __global__ void __launch_bounds__(T, MINB) silu_mul_quant_vec_kernel(
     }
 }
 
-// Persistent form for many rows: a CTA first tabulates the sigmoid of every bf16 gate value in
-// [2^-12, 16) (both signs) in shared memory, then walks rows blockIdx.x, +gridDim.x, ...  The
+// Persistent form for many rows: a CTA first tabulates silu of every bf16 gate value with
+// 2^-12 <= |g| < 2^20 in shared memory, then walks rows blockIdx.x, +gridDim.x, ...  The
 // per-element work drops from ~30 to ~15 issue slots, which is what lets the kernel run at
-// memory speed.  Shared memory: N floats for the row, then the 16 KB table.
+// memory speed.  Shared memory: N floats for the row, then the 32 KB table.
 template <int T, int MINB>
 __global__ void __launch_bounds__(T, MINB) silu_mul_quant_table_kernel(
     const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
@@ -579,9 +579,18 @@ __global__ void __launch_bounds__(1024, 1) silu_mul_quant_async_kernel(
     const float2 one2 = splat2(__int_as_float(0x3f800000 | (N >> 31)));
 
     auto row_active = [&](int row) { return row < M && (mask == nullptr || mask[row] != 0); };
+    // gate_up rows of a packed [M, 2N] tensor follow one another in memory exactly as in the buffer
+    // ([row][gates | ups]): a block of short rows without a mask then comes in with ONE copy
+    const bool block_copy = RPB > 1 && mask == nullptr && u == g + N && ldg == ldu && ldg == 2 * (int64_t)N;
     // the group's first thread: arm the barrier with the bytes to come and start the copies.  The
     // buffer is only ever written by these copies; the kernel reads it.
     auto issue = [&](int rb) {
+        if (block_copy && (rb + 1) * RPB <= M) {
+            const uint32_t all = (uint32_t)RPB * 2u * half_bytes;
+            ptx::mbar_arrive_expect_tx(bar, all);
+            ptx::bulk_load(ptx::smem_u32(my_buf), g + (int64_t)rb * RPB * ldg, all, bar);
+            return;
+        }
         uint32_t bytes = 0;
         for (int r = 0; r < RPB; ++r) bytes += row_active(rb * RPB + r) ? 2u * half_bytes : 0u;
         ptx::mbar_arrive_expect_tx(bar, bytes);

@@ -160,19 +160,24 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 
 // ---- silu by table ------------------------------------------------------------------------
 // The gate is bf16: only 65536 inputs exist.  A kernel may tabulate silu(g) = RN(sigmoid_fixed(g)*g)
-// for the inputs with 2^-12 <= |g| < 16 (2048 bit patterns per sign, 4096 floats = 16 KB of shared
+// for the inputs with 2^-12 <= |g| < 2^20 (4096 bit patterns per sign, 8192 floats = 32 KB of shared
 // memory) and look values up instead of recomputing them; inputs outside that range (zeros,
-// tiny, huge, NaN) are computed.  The table holds the computation's own results, so a lookup
+// tiny, huge, Inf, NaN) are computed.  The table holds the computation's own results, so a lookup
 // returns exactly the same bits.
 constexpr uint32_t kSigTabLo = 0x3980u;    // bf16 bits of 2^-12
-constexpr int kSigTabEntries = 4096;
+constexpr int kSigTabEntries = 8192;
 
-// Entry i < 2048 holds silu(g) = RN(sigmoid_fixed(g) * g) for the positive gate with bf16 bits
-// kSigTabLo + i; entry i >= 2048 the negative gate with magnitude bits kSigTabLo + (4095 - i).
-// With t = gate bits - kSigTabLo (mod 2^16) that is entry (t ^ (sign ? 0xffff : 0)) & 0xfff.
+// Entry i < 4096 holds silu(g) = RN(sigmoid_fixed(g) * g) for the positive gate with bf16 bits
+// kSigTabLo + i; entry i >= 4096 the negative gate with magnitude bits kSigTabLo + (8191 - i).
+// With t = gate bits - kSigTabLo (mod 2^16) that is entry (t ^ (sign ? 0xffff : 0)) & 0x1fff.
+// Two thirds of the range need no exp: for g >= 32, exp_fixed(-g) < 2^-24, so 1 + exp rounds to 1 and
+// sigmoid_fixed(g) is exactly 1 (silu = g); for g <= -88 the exponent argument is clamped, so
+// sigmoid_fixed(g) is the one constant sigmoid_fixed(-88).  Same bits as the general formula.
 __device__ __forceinline__ float silu_table_entry(int i) {
-    const uint32_t bits = i < 2048 ? (kSigTabLo + (uint32_t)i) : (0x8000u | (kSigTabLo + (uint32_t)(4095 - i)));
+    const uint32_t bits = i < 4096 ? (kSigTabLo + (uint32_t)i) : (0x8000u | (kSigTabLo + (uint32_t)(8191 - i)));
     const float g = __uint_as_float(bits << 16);
+    if (g >= 32.0f) return g;
+    if (g <= -88.0f) return __fmul_rn(sigmoid_fixed(-88.0f), g);
     return __fmul_rn(sigmoid_fixed(g), g);
 }
 
@@ -245,7 +250,7 @@ __device__ __forceinline__ uint32_t sign_of_byte1(uint32_t w) {
 // h for the 8 gates / ups of one 16-byte vector pair; tab is the silu table.
 // Both halves of a word are rebased with one subtraction (a borrow out of the low half only happens
 // for a low gate below the table, which is a miss anyway) and one range test covers the vector:
-// a gate hits iff bits 11..14 of its rebased pattern are clear (bit 15 is the sign).  If all 8
+// a gate hits iff bits 12..14 of its rebased pattern are clear (bit 15 is the sign).  If all 8
 // gates hit, silu(g) is looked up, otherwise (rare: zeros, tiny or huge gates) the whole vector is
 // computed.  Both give the same bits.
 __device__ __forceinline__ void silu_mul8_table(const uint4& gv, const uint4& uv, const float* __restrict__ tab,
@@ -255,14 +260,14 @@ __device__ __forceinline__ void silu_mul8_table(const uint4& gv, const uint4& uv
     uint32_t t[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) t[i] = gw[i] - kRebase;
-    if (((t[0] | t[1] | t[2] | t[3]) & 0x78007800u) == 0) {
+    if (((t[0] | t[1] | t[2] | t[3]) & 0x70007000u) == 0) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            // the index is masked to the table's 4096 entries whatever the gate bits are
+            // the index is masked to the table's 8192 entries whatever the gate bits are
             const uint32_t sign_lo = sign_of_byte1(t[i]);
             const uint32_t sign_hi = (uint32_t)((int)t[i] >> 31);
-            const uint32_t lo = (t[i] ^ sign_lo) & 0xfffu;
-            const uint32_t hi = ((t[i] >> 16) ^ sign_hi) & 0xfffu;
+            const uint32_t lo = (t[i] ^ sign_lo) & 0x1fffu;
+            const uint32_t hi = ((t[i] >> 16) ^ sign_hi) & 0x1fffu;
             h[i] = __fmul2_rn(make_float2(tab[lo], tab[hi]), bf16x2_to_f32x2(uw[i]));
         }
     } else {

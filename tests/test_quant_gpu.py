@@ -289,3 +289,14 @@ def test_silu_mul_quant_many_rows_with_mask_and_row_count(cabi, ext):
     _eq(q2[:651], qa, "codes (row count)")
     _eq(s2[:651], sa, "scales (row count)")
     assert q2[651:].abs().sum().item() == 0 and s2[651:].abs().sum().item() == 0
+    # short packed rows (the MoE activation shape): blocks of rows arrive with one copy each; the
+    # device-side row count ends inside a block
+    m, n = 5000, 2048
+    gu = wl.randn_bf16((m, 2 * n), seed=78)
+    gud = gu.cuda()
+    valid = torch.tensor([4099], dtype=torch.int32).cuda()
+    q3 = torch.zeros((m, n), dtype=torch.int8, device="cuda")
+    q3, s3 = ext.silu_mul_quant_rows(gud[:, :n], gud[:, n:], valid)
+    qb, sb = oracle.silu_mul_quant(gu[:4099, :n], gu[:4099, n:])
+    _eq(q3[:4099], qb, "codes (short rows, row count)")
+    _eq(s3[:4099], sb, "scales (short rows, row count)")
