@@ -100,59 +100,116 @@ __global__ void __launch_bounds__(kSegThreads) seg_scatter_kernel(const int* __r
 }
 
 
-// ---- chunked form (R >= 1024 pairs, E <= 1024): one warp per chunk of >= 1024 pairs -----
+// ---- chunked form (R >= 1024 pairs, E <= 1024): one warp per chunk -------------------------
+// The chunk length is 256 pairs for up to 64 experts (short serial loops in the scatter), else 1024.
 // count   : warp b builds the histogram of its chunk in shared memory and parks it in the
 //           chunk's own stretch of dst_slot (dst_slot[chunk_begin + e], e < E <= chunk length)
-// scan    : thread e turns the per-chunk counts of expert e into running bases (in place) and
-//           the totals into exclusive expert offsets
+// scan    : one warp (few experts) or one thread (many) per expert turns the per-chunk counts of
+//           the expert into running bases (in place) and the totals into exclusive expert offsets
 // scatter : warp b reads its bases (before it overwrites that stretch), then numbers its pairs
 //           group of 32 by group of 32 in order, so rows stay sorted by (token, slot)
 // Only a chunk's own warp ever writes its stretch of dst_slot, so the parked counts cannot be
 // clobbered by another chunk; nothing outside the outputs is touched.
-constexpr int kChunk = 1024;
+constexpr int kChunk = 1024;   // longest chunk; the form needs R >= kChunk
 
-__device__ __forceinline__ void chunk_bounds(int b, int nchunks, int R, int& lo, int& hi) {
-    lo = b * kChunk;
-    hi = (b == nchunks - 1) ? R : lo + kChunk;  // the last chunk takes the remainder as well
+__device__ __forceinline__ void chunk_bounds(int b, int nchunks, int chunk, int R, int& lo, int& hi) {
+    lo = b * chunk;
+    hi = (b == nchunks - 1) ? R : lo + chunk;  // the last chunk takes the remainder as well
 }
 
-__global__ void __launch_bounds__(32) seg_chunk_count_kernel(const int* __restrict__ ids, int R, int E,
+// The chunk's expert ids (rebased to the local expert range) go to shared memory first: the loads
+// are independent and issued back to back, where a load inside the match loop would expose a full
+// memory round trip in each of its iterations.  A chunk has fewer than 2 * kChunk pairs.
+__device__ __forceinline__ void stage_chunk_ids(const int* __restrict__ ids, int lo, int hi, int expert_lo, int* sid,
+                                                int lane) {
+#pragma unroll 8
+    for (int i = lo + lane; i < hi; i += 32) sid[i - lo] = __ldg(ids + i) - expert_lo;
+}
+
+__global__ void __launch_bounds__(32) seg_chunk_count_kernel(const int* __restrict__ ids, int R, int E, int chunk,
                                                              int expert_lo, int* __restrict__ dst_slot) {
     __shared__ int hist[1024];
     const int lane = threadIdx.x;
     int lo, hi;
-    chunk_bounds(blockIdx.x, gridDim.x, R, lo, hi);
+    chunk_bounds(blockIdx.x, gridDim.x, chunk, R, lo, hi);
     for (int e = lane; e < E; e += 32) hist[e] = 0;
     __syncwarp();
-    for (int i0 = lo; i0 < hi; i0 += 32) {
-        const int i = i0 + lane;
-        const int e = (i < hi) ? __ldg(ids + i) - expert_lo : -1;
-        const bool in = e >= 0 && e < E;
-        const unsigned act = __ballot_sync(0xffffffffu, in);
-        if (in) {
-            const unsigned m = __match_any_sync(act, e);
-            if (lane == __ffs(m) - 1) hist[e] += __popc(m);
-        }
-        __syncwarp();
+    // counting needs no order: shared-memory atomics, every lane on its own pairs
+#pragma unroll 8
+    for (int i = lo + lane; i < hi; i += 32) {
+        const int e = __ldg(ids + i) - expert_lo;
+        if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
     }
+    __syncwarp();
     for (int e = lane; e < E; e += 32) dst_slot[lo + e] = hist[e];
 }
 
-__global__ void __launch_bounds__(1024) seg_chunk_scan_kernel(int* __restrict__ dst_slot, int nchunks, int E,
+__global__ void __launch_bounds__(1024) seg_chunk_scan_kernel(int* __restrict__ dst_slot, int nchunks, int chunk, int E,
                                                               int* __restrict__ offsets) {
+    __shared__ int totals[1024];
+    __shared__ int warp_sums[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    totals[tid] = 0;
+    __syncthreads();
+    // warp w: experts w, w + 32, ...; lane = chunk (32 chunks per round, carried over the rounds)
+    for (int e = warp; e < E; e += 32) {
+        int run = 0;
+        // four rounds of 32 chunks per batch: the loads of a batch are independent of the running sum
+        for (int b0 = 0; b0 < nchunks; b0 += 128) {
+            int c[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int b = b0 + 32 * j + lane;
+                c[j] = b < nchunks ? dst_slot[(int64_t)b * chunk + e] : 0;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int b = b0 + 32 * j + lane;
+                const int incl = warp_incl_scan(c[j], lane);
+                if (b < nchunks) dst_slot[(int64_t)b * chunk + e] = run + incl - c[j];  // rows of expert e from earlier chunks
+                run += __shfl_sync(0xffffffffu, incl, 31);
+            }
+        }
+        if (lane == 0) totals[e] = run;
+    }
+    __syncthreads();
+    // exclusive scan of the totals over the experts
+    const int e = tid;
+    int incl = warp_incl_scan(totals[e], lane);
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const int ws = warp_sums[lane];
+        const int wi = warp_incl_scan(ws, lane);
+        warp_sums[lane] = wi - ws;
+    }
+    __syncthreads();
+    const int excl = warp_sums[warp] + incl - totals[e];
+    if (e < E) offsets[e] = excl;
+    if (e == E - 1) offsets[E] = excl + totals[e];
+}
+
+// The same scan with one THREAD per expert (consecutive experts = consecutive addresses), for many
+// experts: eight chunks at a time, the loads of a batch are independent of the running sum.
+__global__ void __launch_bounds__(1024) seg_chunk_scan_wide_kernel(int* __restrict__ dst_slot, int nchunks, int chunk,
+                                                                   int E, int* __restrict__ offsets) {
     __shared__ int totals[1024];
     __shared__ int warp_sums[32];
     const int e = threadIdx.x;
     int run = 0;
     if (e < E) {
-        for (int b = 0; b < nchunks; ++b) {
-            const int c = dst_slot[b * kChunk + e];
-            dst_slot[b * kChunk + e] = run;  // rows of expert e that earlier chunks contribute
-            run += c;
+        for (int b0 = 0; b0 < nchunks; b0 += 8) {
+            int c[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) c[j] = (b0 + j < nchunks) ? dst_slot[(int64_t)(b0 + j) * chunk + e] : 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (b0 + j < nchunks) dst_slot[(int64_t)(b0 + j) * chunk + e] = run;
+                run += c[j];
+            }
         }
     }
     totals[e] = (e < E) ? run : 0;
-    // exclusive scan of the totals over the experts
     const int lane = e & 31, warp = e >> 5;
     int incl = warp_incl_scan(totals[e], lane);
     if (lane == 31) warp_sums[warp] = incl;
@@ -169,17 +226,19 @@ __global__ void __launch_bounds__(1024) seg_chunk_scan_kernel(int* __restrict__ 
 }
 
 __global__ void __launch_bounds__(32) seg_chunk_scatter_kernel(const int* __restrict__ ids, int R, int topk, int E,
-                                                               int expert_lo, const int* __restrict__ offsets,
+                                                               int chunk, int expert_lo, const int* __restrict__ offsets,
                                                                int* __restrict__ src_row, int* __restrict__ dst_slot) {
     __shared__ int base[1024];
+    __shared__ int sid[2 * kChunk];
     const int lane = threadIdx.x;
     int lo, hi;
-    chunk_bounds(blockIdx.x, gridDim.x, R, lo, hi);
+    chunk_bounds(blockIdx.x, gridDim.x, chunk, R, lo, hi);
     for (int e = lane; e < E; e += 32) base[e] = offsets[e] + dst_slot[lo + e];
+    stage_chunk_ids(ids, lo, hi, expert_lo, sid, lane);
     __syncwarp();
     for (int i0 = lo; i0 < hi; i0 += 32) {
         const int i = i0 + lane;
-        const int e = (i < hi) ? __ldg(ids + i) - expert_lo : -1;
+        const int e = (i < hi) ? sid[i - lo] : -1;
         const bool in = e >= 0 && e < E;
         const unsigned act = __ballot_sync(0xffffffffu, in);
         if (in) {
@@ -450,10 +509,18 @@ int moe_segments(const int* topk_ids, int T, int topk, int E, int expert_lo, int
     if (R64 > INT32_MAX) return fail(DSV4_ERR_ARG, "moe_segments: T*topk exceeds int32");
     const int R = (int)R64;
     if (R >= kChunk && E <= 1024) {
-        const int nchunks = R / kChunk;
-        seg_chunk_count_kernel<<<nchunks, 32, 0, st>>>(topk_ids, R, E, expert_lo, dst_slot);
-        seg_chunk_scan_kernel<<<1, 1024, 0, st>>>(dst_slot, nchunks, E, offsets);
-        seg_chunk_scatter_kernel<<<nchunks, 32, 0, st>>>(topk_ids, R, topk, E, expert_lo, offsets, src_row, dst_slot);
+        // few experts (an expert-parallel rank): short chunks, one warp per expert in the scan; many
+        // experts: long chunks, one thread per expert
+        const bool few = E <= 64;
+        const int chunk = few ? 256 : kChunk;
+        const int nchunks = R / chunk;
+        seg_chunk_count_kernel<<<nchunks, 32, 0, st>>>(topk_ids, R, E, chunk, expert_lo, dst_slot);
+        if (few)
+            seg_chunk_scan_kernel<<<1, 1024, 0, st>>>(dst_slot, nchunks, chunk, E, offsets);
+        else
+            seg_chunk_scan_wide_kernel<<<1, 1024, 0, st>>>(dst_slot, nchunks, chunk, E, offsets);
+        seg_chunk_scatter_kernel<<<nchunks, 32, 0, st>>>(topk_ids, R, topk, E, chunk, expert_lo, offsets, src_row,
+                                                         dst_slot);
         return check_launch("moe_segments");
     }
     seg_count_kernel<<<E, kSegThreads, 0, st>>>(topk_ids, R, expert_lo, offsets, dst_slot);
@@ -469,7 +536,13 @@ int gather_rows(const void* src, const int* src_row, void* dst, int R, int row_b
     if (src == nullptr || dst == nullptr || src_row == nullptr) return fail(DSV4_ERR_ARG, "gather_rows: null pointer");
     if ((reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15))
         return fail(DSV4_ERR_ARG, "gather_rows: src and dst must be 16-byte aligned");
-    gather_rows_kernel<<<R, 128, 0, st>>>(static_cast<const uint4*>(src), src_row, static_cast<uint4*>(dst), R,
+    // With a device-side row count most of the R CTAs would find nothing to do; a grid of a few CTAs
+    // per SM walks the rows instead.
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = (sms > 0 && R > 16 * sms) ? 16 * sms : R;
+    gather_rows_kernel<<<grid, 128, 0, st>>>(static_cast<const uint4*>(src), src_row, static_cast<uint4*>(dst), R,
                                           row_bytes / 16, src_scale, dst_scale, scales_per_row, valid_rows);
     return check_launch("gather_rows");
 }

@@ -8,7 +8,8 @@ from oracle import cpu as oracle
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("t,e,topk", [(4096, 256, 8), (1, 256, 8), (77, 16, 2), (1000, 5, 1), (300, 64, 6)])
+@pytest.mark.parametrize("t,e,topk", [(4096, 256, 8), (1, 256, 8), (77, 16, 2), (1000, 5, 1), (300, 64, 6),
+                                      (700, 384, 8), (1500, 1000, 3), (4099, 32, 8), (9000, 257, 5)])
 def test_moe_segments_match_oracle(cabi, ext, t, e, topk):
     ids, _ = wl.moe_routing(t, e, topk, seed=t + e)
     off_ref, src_ref, dst_ref = oracle.moe_segments(ids, e)
@@ -37,7 +38,8 @@ def test_gather_rows(cabi, ext):
     assert torch.equal(out[0].cpu().view(torch.int16), xb[idx.long()].view(torch.int16))
 
 
-@pytest.mark.parametrize("t,e,topk,lo,n_local", [(300, 64, 6, 16, 16), (77, 16, 2, 8, 8), (64, 8, 2, 0, 4)])
+@pytest.mark.parametrize("t,e,topk,lo,n_local", [(300, 64, 6, 16, 16), (77, 16, 2, 8, 8), (64, 8, 2, 0, 4),
+                                                 (4096, 256, 8, 96, 32), (2000, 640, 4, 320, 320)])
 def test_moe_segments_expert_slice(cabi, ext, t, e, topk, lo, n_local):
     ids, _ = wl.moe_routing(t, e, topk, seed=t)
     off_ref, src_ref, dst_ref = oracle.moe_segments(ids, n_local, lo)
