@@ -280,36 +280,81 @@ __global__ void __launch_bounds__(128) moe_combine_kernel(const __nv_bfloat16* _
                                                           const int* __restrict__ dst_slot,
                                                           const float* __restrict__ w, void* __restrict__ out, int T,
                                                           int topk, int H) {
+    constexpr int kBatch = 8;                   // expert rows in flight per thread
+    __shared__ const uint4* rowp[kBatch];
+    __shared__ float wk[kBatch];
     const int V = H >> 3;
-    for (int t = blockIdx.x; t < T; t += gridDim.x) {
-        for (int v = threadIdx.x; v < V; v += blockDim.x) {
-            float acc[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
-            for (int j = 0; j < topk; ++j) {
+    const bool one_batch = topk <= kBatch;      // the usual case: the row pointers are set up once per token
+    auto load_rows = [&](int t, int j0) {
+        if (threadIdx.x < kBatch) {
+            const int j = j0 + threadIdx.x;
+            const uint4* ptr = nullptr;
+            float wj = 0.0f;
+            if (j < topk) {
                 const int slot = __ldg(dst_slot + (int64_t)t * topk + j);
-                if (slot < 0) continue;
-                const float wj = __ldg(w + (int64_t)t * topk + j);
-                const uint4 zv = __ldg(reinterpret_cast<const uint4*>(z + (int64_t)slot * H) + v);
-                const uint32_t zw[4] = {zv.x, zv.y, zv.z, zv.w};
+                wj = __ldg(w + (int64_t)t * topk + j);
+                if (slot >= 0) ptr = reinterpret_cast<const uint4*>(z + (int64_t)slot * H);
+            }
+            rowp[threadIdx.x] = ptr;
+            wk[threadIdx.x] = wj;
+        }
+    };
+    for (int t = blockIdx.x; t < T; t += gridDim.x) {
+        if (one_batch) {
+            load_rows(t, 0);
+            __syncthreads();
+        }
+        for (int vb = 0; vb < V; vb += 2 * 128) {
+            float acc[2][8];                    // up to two 16-byte vectors per thread and pass
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    acc[2 * e] = __fmaf_rn(wj, __uint_as_float(zw[e] << 16), acc[2 * e]);
-                    acc[2 * e + 1] = __fmaf_rn(wj, __uint_as_float(zw[e] & 0xffff0000u), acc[2 * e + 1]);
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[i][e] = 0.0f;
+            for (int j0 = 0; j0 < topk; j0 += kBatch) {
+                if (!one_batch) {
+                    __syncthreads();            // the previous batch's pointers have been used
+                    load_rows(t, j0);
+                    __syncthreads();
+                }
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int v = vb + i * 128 + threadIdx.x;
+                    if (v >= V) break;
+                    uint4 zv[kBatch];
+#pragma unroll
+                    for (int j = 0; j < kBatch; ++j)
+                        zv[j] = rowp[j] != nullptr ? __ldg(rowp[j] + v) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                    for (int j = 0; j < kBatch; ++j) {
+                        if (rowp[j] == nullptr) continue;   // a skipped slot adds nothing, not even +0
+                        const float wj = wk[j];
+                        const uint32_t zw[4] = {zv[j].x, zv[j].y, zv[j].z, zv[j].w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            acc[i][2 * e] = __fmaf_rn(wj, __uint_as_float(zw[e] << 16), acc[i][2 * e]);
+                            acc[i][2 * e + 1] = __fmaf_rn(wj, __uint_as_float(zw[e] & 0xffff0000u), acc[i][2 * e + 1]);
+                        }
+                    }
                 }
             }
-            if (OUT_F32) {
-                float4* o = reinterpret_cast<float4*>(static_cast<float*>(out) + (int64_t)t * H) + 2 * v;
-                o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-            } else {
-                __nv_bfloat162 b[4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) b[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
-                reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(out) + (int64_t)t * H)[v] =
-                    *reinterpret_cast<uint4*>(b);
+            for (int i = 0; i < 2; ++i) {
+                const int v = vb + i * 128 + threadIdx.x;
+                if (v >= V) break;
+                if (OUT_F32) {
+                    float4* o = reinterpret_cast<float4*>(static_cast<float*>(out) + (int64_t)t * H) + 2 * v;
+                    o[0] = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+                    o[1] = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+                } else {
+                    __nv_bfloat162 b[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) b[e] = __floats2bfloat162_rn(acc[i][2 * e], acc[i][2 * e + 1]);
+                    reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(out) + (int64_t)t * H)[v] =
+                        *reinterpret_cast<uint4*>(b);
+                }
             }
         }
+        __syncthreads();
     }
 }
 
