@@ -146,7 +146,7 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launch
     torch.cuda.empty_cache()
 
     try:
-        res["moe_ffn T=4096 E=256 I=2048 top8"] = _moe_section(ext, dev, rank, world, peaks, time_launches)
+        res["moe_ffn T=4096 E=256 I=2048 top8"] = _moe_section(ext, dev, rank, world, peaks, time_launches, time_launches_graph)
     except Exception as exc:  # pragma: no cover
         res["moe_ffn"] = {"error": f"{type(exc).__name__}: {exc}"}
     torch.cuda.empty_cache()
@@ -174,7 +174,7 @@ def _sync(world):
     torch.cuda.synchronize()
 
 
-def _moe_section(ext, dev, rank, world, peaks, time_launches):
+def _moe_section(ext, dev, rank, world, peaks, time_launches, time_launches_graph=None):
     """MoE FFN, experts sharded over the ranks (expert parallel), tokens and routing replicated.
     Weight-bandwidth-bound: ~128 routed rows per expert against 44 MB of int8 weights per expert."""
     from . import moe
@@ -230,7 +230,10 @@ def _moe_section(ext, dev, rank, world, peaks, time_launches):
         "grouped_gemm down": lambda i: ext.grouped_gemm(tr.h_q, inp.w2, tr.h_s, inp.w2_scale, tr.offsets),
         "moe_combine": lambda i: ext.moe_combine(tr.z, tr.dst_slot, inp.topk_w, False),
     }
-    out["stages_us_rank0"] = {k: round(1e3 * time_launches(f, 10, warmup=2), 1) for k, f in stages.items()}
+    if time_launches_graph is not None:   # device time per launch from CUDA-graph replays
+        out["stages_us_rank0"] = {k: round(1e3 * time_launches_graph(f, 10, 5), 1) for k, f in stages.items()}
+    else:
+        out["stages_us_rank0"] = {k: round(1e3 * time_launches(f, 10, warmup=2), 1) for k, f in stages.items()}
     return out
 
 
