@@ -573,6 +573,54 @@ def run_single_kernel(args):
         xs = [wl.randn_bf16((m, K), device=dev, seed=i) for i in range(nsets)]
         fn = lambda i: ext.per_token_group_quant_int8(xs[i % nsets], 128)
         work = {"bytes": 3 * m * K + 4 * m * (K // 128)}
+    elif args.kernel == "rmsnorm":
+        xs = [wl.randn_bf16((m, K), device=dev, seed=i) for i in range(nsets)]
+        fn = lambda i: ext.rmsnorm(xs[i % nsets], 1e-6)
+        work = {"bytes": 4 * m * K}
+    elif args.kernel == "silu_and_mul":
+        gus = [wl.randn_bf16((m, 2 * I), device=dev, seed=i) for i in range(nsets)]
+        fn = lambda i: ext.silu_and_mul(gus[i % nsets][:, :I], gus[i % nsets][:, I:])
+        work = {"bytes": 6 * m * I}
+    elif args.kernel in ("moe_topk", "moe_segments", "gather_rows", "moe_combine", "moe_combine_exchange"):
+        # the MoE front and back end at the configuration's sizes: T tokens, 256 experts, top-8
+        T, E, topk, H = wl.MOE_TOKENS, wl.MOE_EXPERTS, wl.MOE_TOPK, K
+        gen = torch.Generator(device=dev).manual_seed(0)
+        logits = torch.randn((T, E), device=dev, generator=gen)
+        ids, w = ext.moe_topk(logits, topk)
+        off, src_row, dst_slot = ext.moe_segments(ids, E, 0)
+        if args.kernel == "moe_topk":
+            fn = lambda i: ext.moe_topk(logits, topk)
+            work = {"bytes": 4 * T * E + 8 * T * topk}
+        elif args.kernel == "moe_segments":
+            fn = lambda i: ext.moe_segments(ids, E, 0)
+            work = {"bytes": 4 * T * topk * 4}
+        elif args.kernel == "gather_rows":
+            q = wl.int8_weights((T, H), device=dev, seed=1)
+            sg = wl.channel_scales((T, H // 128), device=dev, seed=2)
+            fn = lambda i: ext.gather_rows(q, src_row, sg, None)
+            work = {"bytes": T * topk * (2 * H + 8 * (H // 128))}
+        else:
+            zs = [wl.randn_bf16((T * topk, H), device=dev, seed=i) for i in range(2)]
+            if args.kernel == "moe_combine":
+                fn = lambda i: ext.moe_combine(zs[i % 2], dst_slot, w, False)
+            else:
+                # one rank's call of the fused combine + exchange with every pointer local: all tokens,
+                # one output buffer (the kernel only sees pointers)
+                outb = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+                fn = lambda i: ext.moe_combine_exchange([zs[i % 2].data_ptr()], [dst_slot.data_ptr()], ids, w,
+                                                        [outb.data_ptr()], E, 0, T, H)
+            work = {"bytes": 2 * T * topk * H + 2 * T * H}
+    elif args.kernel == "gemm_allgather":
+        # the CTA-pair GEMM with the fused all-gather epilogue (TMA tile stores), two local buffers
+        # standing in for this rank's and one peer's output
+        A = [wl.int8_weights((m, K), device=dev, seed=i) for i in range(nsets)]
+        W = [wl.int8_weights((N, K), device=dev, seed=10 + i) for i in range(nsets)]
+        sa = wl.channel_scales((m,), device=dev, seed=1)
+        sb = wl.channel_scales((N,), device=dev, seed=2)
+        out0 = torch.empty((m, 2 * N), dtype=torch.bfloat16, device=dev)
+        out1 = torch.empty((m, 2 * N), dtype=torch.bfloat16, device=dev)
+        fn = lambda i: ext.w8a8_gemm_allgather(A[i % nsets], W[i % nsets], sa, sb, out0, N, [out1.data_ptr()])
+        work = {"ops": 2.0 * m * N * K, "bytes": gemm_bytes(m, N, K) + 2 * m * N}
     else:
         raise SystemExit(f"unknown --kernel {args.kernel}")
     ms = time_launches(fn, args.steps, warmup=max(1, args.warmup))
@@ -589,8 +637,9 @@ def run_single_kernel(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default=None,
-                    help="run one kernel only: gemm, gemm_down, grouped, grouped_gs, add_rmsnorm_quant, "
-                         "silu_mul_quant, ptq, ptgq")
+                    help="run one kernel only: gemm, gemm_down, gemm_allgather, grouped, grouped_gs, "
+                         "add_rmsnorm_quant, silu_mul_quant, ptq, ptgq, rmsnorm, silu_and_mul, moe_topk, moe_segments, "
+                         "gather_rows, moe_combine, moe_combine_exchange")
     ap.add_argument("--m", type=int, default=M_ROWS, help="rows for --kernel")
     ap.add_argument("--graph", action="store_true", help="with --kernel: also time CUDA-graph replays")
     ap.add_argument("--gpus", type=int, default=1)

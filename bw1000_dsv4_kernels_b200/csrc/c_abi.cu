@@ -128,6 +128,17 @@ int launch_silu_mul(const void* g, const void* u, void* out, int M, int N, dsv4_
     return silu_mul(g, u, out, M, N, N, N, cs(stream));
 }
 
+int launch_silu_mul_strided(const void* g, long long ldg, const void* u, long long ldu, void* out, int M, int N,
+                            dsv4_stream_t stream) {
+    if (int rc = check_rows("silu_and_mul", M, N)) return rc;
+    if (M == 0 || N == 0) return 0;
+    DSV4_REQUIRE_PTR("silu_and_mul", g);
+    DSV4_REQUIRE_PTR("silu_and_mul", u);
+    DSV4_REQUIRE_PTR("silu_and_mul", out);
+    if (ldg < N || ldu < N) return fail(DSV4_ERR_ARG, "silu_and_mul: row stride smaller than N");
+    return silu_mul(g, u, out, M, N, ldg, ldu, cs(stream));
+}
+
 int launch_w8a8_gemm(const void* A, const void* B, const void* sa, const void* sb, void* C, int M, int N, int K,
                      dsv4_stream_t stream) {
     GemmArgs a{};

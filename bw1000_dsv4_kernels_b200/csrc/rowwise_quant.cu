@@ -741,6 +741,40 @@ __global__ void __launch_bounds__(256) silu_mul_vec_kernel(const __nv_bfloat16* 
     }
 }
 
+// Many elements: persistent CTAs that tabulate silu of every bf16 gate first (silu_mul8_table), then
+// walk rows blockIdx.x, +gridDim.x, ...; the vectors of a row are dealt to the threads, two in flight
+// per thread.  Same bits as silu_mul for every input.
+__global__ void __launch_bounds__(512, 2) silu_mul_table_kernel(const __nv_bfloat16* __restrict__ g,
+                                                                const __nv_bfloat16* __restrict__ u,
+                                                                __nv_bfloat16* __restrict__ out, int M, int N,
+                                                                int64_t ldg, int64_t ldu) {
+    __shared__ float tab[kSigTabEntries];
+    for (int i = threadIdx.x; i < kSigTabEntries; i += 512) tab[i] = silu_table_entry(i);
+    __syncthreads();
+    const int V = N >> 3;
+    for (int row = blockIdx.x; row < M; row += gridDim.x) {
+        const uint4* gr = reinterpret_cast<const uint4*>(g + (int64_t)row * ldg);
+        const uint4* ur = reinterpret_cast<const uint4*>(u + (int64_t)row * ldu);
+        uint4* orow = reinterpret_cast<uint4*>(out + (int64_t)row * N);
+        for (int i0 = threadIdx.x; i0 < V; i0 += 2 * 512) {
+            const int i1 = i0 + 512;
+            const bool two = i1 < V;
+            const uint4 g0 = ld_stream(gr + i0), u0 = ld_stream(ur + i0);
+            const uint4 g1 = two ? ld_stream(gr + i1) : make_uint4(0, 0, 0, 0);
+            const uint4 u1 = two ? ld_stream(ur + i1) : make_uint4(0, 0, 0, 0);
+            float2 h[4];
+            silu_mul8_table(g0, u0, tab, h);
+            orow[i0] = make_uint4(pack_bf16x2_rn(h[0].x, h[0].y), pack_bf16x2_rn(h[1].x, h[1].y),
+                                  pack_bf16x2_rn(h[2].x, h[2].y), pack_bf16x2_rn(h[3].x, h[3].y));
+            if (two) {
+                silu_mul8_table(g1, u1, tab, h);
+                orow[i1] = make_uint4(pack_bf16x2_rn(h[0].x, h[0].y), pack_bf16x2_rn(h[1].x, h[1].y),
+                                      pack_bf16x2_rn(h[2].x, h[2].y), pack_bf16x2_rn(h[3].x, h[3].y));
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256) silu_mul_generic_kernel(const __nv_bfloat16* __restrict__ g,
                                                                const __nv_bfloat16* __restrict__ u,
                                                                __nv_bfloat16* __restrict__ out,
@@ -976,7 +1010,12 @@ int silu_mul(const void* g, const void* u, void* out, int M, int N, int64_t ldg,
     const int64_t work = vec ? (int64_t)M * (N / 8) : (int64_t)M * N;
     int64_t blocks = (work + 255) / 256;
     if (blocks > (1 << 20)) blocks = 1 << 20;
-    if (vec)
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (vec && sms > 0 && (int64_t)M * N >= (int64_t)(1 << 21) && M >= 2 * sms)
+        silu_mul_table_kernel<<<2 * sms, 512, 0, st>>>(gp, up, op, M, N, ldg, ldu);
+    else if (vec)
         silu_mul_vec_kernel<<<(int)blocks, 256, 0, st>>>(gp, up, op, M, N, ldg, ldu);
     else
         silu_mul_generic_kernel<<<(int)blocks, 256, 0, st>>>(gp, up, op, M, N, ldg, ldu);

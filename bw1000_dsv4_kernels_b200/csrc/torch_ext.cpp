@@ -124,12 +124,8 @@ Tensor silu_and_mul_stream(Tensor gate, Tensor up, int64_t stream_ptr) {
     const GateUp g = check_gate_up(gate, up);
     c10::cuda::CUDAGuard guard(gate.device());
     auto out = torch::empty({g.M, g.N}, gate.options());
-    if (g.ldg == g.N && g.ldu == g.N) {
-        check_status(launch_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(), g.M, g.N, as_stream(stream_ptr)));
-    } else {
-        auto gc = gate.contiguous(), uc = up.contiguous();
-        check_status(launch_silu_mul(gc.data_ptr(), uc.data_ptr(), out.data_ptr(), g.M, g.N, as_stream(stream_ptr)));
-    }
+    check_status(launch_silu_mul_strided(gate.data_ptr(), g.ldg, up.data_ptr(), g.ldu, out.data_ptr(), g.M, g.N,
+                                         as_stream(stream_ptr)));
     return out;
 }
 
@@ -146,14 +142,15 @@ std::vector<Tensor> silu_mul_quant_stream(Tensor gate, Tensor up, int64_t stream
 
 // Same, but only the first min(M, valid_rows[0]) rows are processed; valid_rows is a one-element
 // int32 CUDA tensor (the routed-row count of an expert-parallel rank lives on the device).
-// Rows beyond it are returned as zero.
+// Rows beyond it are left unwritten (their content is unspecified, as in gather_rows): a zero fill
+// of the whole [M, N] output would cost more than the kernel when few rows are valid.
 std::vector<Tensor> silu_mul_quant_rows_stream(Tensor gate, Tensor up, Tensor valid_rows, int64_t stream_ptr) {
     const GateUp g = check_gate_up(gate, up);
     check_cuda(valid_rows, "valid_rows", torch::kInt32);
     TORCH_CHECK(valid_rows.numel() >= 1, "valid_rows must hold one int32");
     c10::cuda::CUDAGuard guard(gate.device());
-    auto q = torch::zeros({g.M, g.N}, gate.options().dtype(torch::kInt8));
-    auto s = torch::zeros({g.M}, gate.options().dtype(torch::kFloat32));
+    auto q = torch::empty({g.M, g.N}, gate.options().dtype(torch::kInt8));
+    auto s = torch::empty({g.M}, gate.options().dtype(torch::kFloat32));
     check_status(launch_silu_mul_quant_strided(gate.data_ptr(), g.ldg, up.data_ptr(), g.ldu, nullptr,
                                                static_cast<const int*>(valid_rows.data_ptr()), q.data_ptr(),
                                                s.data_ptr(), g.M, g.N, as_stream(stream_ptr)));

@@ -111,6 +111,11 @@ DSV4_API int launch_rmsnorm_self(void* x, int M, int N, float eps, dsv4_stream_t
 
 /* out = bf16(silu(g) * u).  Replaces launch_silu_mul, dsv4_all_hip_kernels.hip:359-361. */
 DSV4_API int launch_silu_mul(const void* g, const void* u, void* out, int M, int N, dsv4_stream_t stream);
+/* Same with row strides ldg / ldu (elements) for gate and up, e.g. the two halves of a packed
+ * gate_up [M, 2N] tensor as the reference's wrapper slices them (dsv4_native_ext.cpp:327-346);
+ * out is dense [M, N]. */
+DSV4_API int launch_silu_mul_strided(const void* g, long long ldg, const void* u, long long ldu, void* out, int M,
+                       int N, dsv4_stream_t stream);
 
 /* ---- int8 GEMM ------------------------------------------------------------------ */
 
