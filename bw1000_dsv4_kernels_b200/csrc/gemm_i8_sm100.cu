@@ -117,7 +117,7 @@ template <int BN, int STAGES>
 int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, int max_tiles,
                    cudaStream_t st) {
     using L = Smem<BN, STAGES>;
-    static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
+    static_assert(L::kDynamic <= 227 * 1024, "shared memory limit");
     static bool opted_in[64] = {};
     if (!opt_in_shared_memory(gemm_i8_kernel<BN, STAGES>, L::kDynamic, opted_in))
         return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: cannot raise the dynamic shared memory limit");
@@ -133,7 +133,7 @@ template <int NTOK>
 int launch_stream_variant(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, int n_tiles, int splits,
                           cudaStream_t st) {
     using L = StreamSmem<NTOK>;
-    static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
+    static_assert(L::kDynamic <= 227 * 1024, "shared memory limit");
     static bool opted_in[64] = {};
     if (!opt_in_shared_memory(gemm_i8_stream_kernel<NTOK>, L::kDynamic, opted_in))
         return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: cannot raise the dynamic shared memory limit");
@@ -192,7 +192,7 @@ int stream_pair_active_clusters(int splits) {
 int launch_stream_pair(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, int n_tiles, int splits,
                        cudaStream_t st) {
     using L = StreamPairSmem;
-    static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
+    static_assert(L::kDynamic <= 227 * 1024, "shared memory limit");
     static bool opted_in[64] = {};
     if (!opt_in_shared_memory(gemm_i8_stream_pair_kernel, L::kDynamic, opted_in))
         return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: cannot raise the dynamic shared memory limit");
@@ -225,7 +225,7 @@ int launch_stream_pair(const CUtensorMap& tmW, const CUtensorMap& tmX, const Par
 template <int STAGES>
 int launch_gs_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, int max_tiles, cudaStream_t st) {
     using L = Smem<GSN, STAGES>;
-    static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
+    static_assert(L::kDynamic <= 227 * 1024, "shared memory limit");
     static bool opted_in[64] = {};
     if (!opt_in_shared_memory(gemm_i8_gs_kernel<STAGES>, L::kDynamic, opted_in))
         return fail(DSV4_ERR_LAUNCH, "grouped_gemm: cannot raise the dynamic shared memory limit");
@@ -256,7 +256,7 @@ template <int STAGES, bool TMA_STORE>
 int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, const StoreMaps& smaps,
                         cudaStream_t st) {
     using L = PairSmem<STAGES, TMA_STORE>;
-    static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
+    static_assert(L::kDynamic <= 227 * 1024, "shared memory limit");
     static bool opted_in[64] = {};
     if (!opt_in_shared_memory(gemm_i8_pair_kernel<STAGES, TMA_STORE>, L::kDynamic, opted_in))
         return fail(DSV4_ERR_LAUNCH, "w8a8_gemm: cannot raise the dynamic shared memory limit");

@@ -99,8 +99,8 @@ struct StreamSmem {
     static constexpr int kWBytes = 128 * BK;
     static constexpr int kXBytes = NTOK * BK;
     static constexpr int kStageBytes = kWBytes + kXBytes;
-    static constexpr int kBudget = 196 * 1024;
-    static constexpr int kStages = kBudget / kStageBytes;
+    static constexpr int kRingBytes = 196 * 1024;
+    static constexpr int kStages = kRingBytes / kStageBytes;
     static constexpr int kTilesBytes = kStages * kStageBytes;
     static constexpr int kPartialBytes = NTOK * 128 * 4;
     static_assert(kPartialBytes <= kTilesBytes, "the partial tile reuses the stage ring");
