@@ -35,6 +35,34 @@ __device__ __forceinline__ uint4 ld_stream(const uint4* p) {
 }
 __device__ __forceinline__ uint4 ld_plain(const uint4* p) { return *p; }
 
+// L2 eviction policy "evict first" for data that is touched once (activations streaming through a row
+// kernel), so that it does not push a concurrently running GEMM's operand tiles out of L2.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint4 ld_stream_once(const uint4* p, uint64_t pol) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ uint4 ld_plain_once(const uint4* p, uint64_t pol) {
+    uint4 v;
+    asm volatile("ld.global.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p), "l"(pol)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_once(uint4* p, const uint4& v, uint64_t pol) {
+    asm volatile("st.global.L2::cache_hint.v4.u32 [%0], {%1,%2,%3,%4}, %5;" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+                 "r"(v.w), "l"(pol)
+                 : "memory");
+}
+
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
     f[0] = bf16lo_to_f32(v.x); f[1] = bf16hi_to_f32(v.x);
     f[2] = bf16lo_to_f32(v.y); f[3] = bf16hi_to_f32(v.y);
@@ -228,6 +256,7 @@ __global__ void __launch_bounds__(kSumLanes) add_rmsnorm_quant_vec_kernel(
     __shared__ float red_sum[8];
     __shared__ float red_max[32];
     const int V = K >> 3, tid = threadIdx.x;
+    const uint64_t once = l2_evict_first_policy();  // x and the residual pass through L2 once
     for (int row = blockIdx.x; row < M; row += gridDim.x) {
         uint4* rr = reinterpret_cast<uint4*>(res + (int64_t)row * K);
         const uint4* xr = reinterpret_cast<const uint4*>(x + (int64_t)row * K);
@@ -237,8 +266,8 @@ __global__ void __launch_bounds__(kSumLanes) add_rmsnorm_quant_vec_kernel(
         for (int i = 0; i < VPT; ++i) {
             const int idx = tid + i * kSumLanes;
             if (idx < V) {
-                rv[i] = ld_plain(rr + idx);  // written back below: keep it on the coherent path
-                xv[i] = ld_stream(xr + idx);
+                rv[i] = ld_plain_once(rr + idx, once);  // written back below: keep it on the coherent path
+                xv[i] = ld_stream_once(xr + idx, once);
             } else {
                 rv[i] = make_uint4(0, 0, 0, 0);
                 xv[i] = make_uint4(0, 0, 0, 0);
@@ -263,7 +292,7 @@ __global__ void __launch_bounds__(kSumLanes) add_rmsnorm_quant_vec_kernel(
                 o.y = pack_bf16x2_rn(a[i][2], a[i][3]);
                 o.z = pack_bf16x2_rn(a[i][4], a[i][5]);
                 o.w = pack_bf16x2_rn(a[i][6], a[i][7]);
-                rr[idx] = o;
+                st_once(rr + idx, o, once);
             }
         }
         const float total = block_sum_256(ss, red_sum);
