@@ -262,3 +262,49 @@ def test_gemm_fused_allgather_tile_store_path(cabi, ext, m, n):
     for b in bufs:
         assert torch.equal(b[:, col0:col0 + n].cpu().view(torch.int16), ref.view(torch.int16))
         assert (b[:, :col0] == 5.0).all() and (b[:, col0 + n:] == 5.0).all()
+
+
+def test_tp_linear_full_size_shards_equal_the_whole(ext):
+    # the column-sharded configuration at its full size (M=8192, K=7168, N=28672) on one device: the
+    # eight ranks' slabs, each from that rank's own seeded weight shard and written into its column
+    # range, give the bits of the unsharded layer (columns are independent: a size-independent
+    # property); a sampled block of rows and columns is also checked against the oracle
+    from bw1000_dsv4_kernels_b200 import tp_linear
+    dev = torch.device("cuda")
+    m, k, n, world = wl.TP_M, wl.HIDDEN, wl.TP_N, 8
+    full = wl.tp_linear_inputs(0, 1, m=m, k=k, n=n, device=dev, seed=0)
+    whole = tp_linear.ColumnParallelW8A8Linear(full.w, full.w_scale).forward(full.x)
+    q, s = ext.per_token_quant_int8(full.x)
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    per = n // world
+    for r in range(world):
+        shard = wl.tp_linear_inputs(r, world, m=m, k=k, n=n, device=dev, seed=0)
+        assert torch.equal(shard.w, full.w[r * per:(r + 1) * per])
+        ext.w8a8_gemm_into(q, shard.w, s, shard.w_scale, out, r * per)
+    assert torch.equal(out.view(torch.int16), whole.view(torch.int16))
+    rows, cols = slice(4000, 4064), slice(per * 3 - 32, per * 3 + 32)    # straddles two ranks' slabs
+    q_ref, s_ref = oracle.per_token_quant_int8(full.x[rows].cpu())
+    ref = oracle.w8a8_gemm(q_ref, full.w[cols].cpu(), s_ref.view(-1), full.w_scale[cols].cpu())
+    assert torch.equal(whole[rows, cols].cpu().contiguous().view(torch.int16), ref.view(torch.int16))
+
+
+def test_down_projection_chain_full_size_sampled(ext):
+    # silu_mul_quant -> down-projection GEMM at the configuration's largest size (M=8192, N=18432 ->
+    # 7168): every row's codes and scale are checked against the oracle on sampled rows (rows are
+    # independent), the GEMM on a sampled block of rows and columns
+    dev = torch.device("cuda")
+    m, inter, h = 8192, wl.DENSE_INTER, wl.HIDDEN
+    gu = wl.randn_bf16((m, 2 * inter), device=dev, seed=3)
+    w = wl.int8_weights((h, inter), device=dev, seed=4)
+    ws = wl.channel_scales((h,), device=dev, seed=5)
+    q, s = ext.silu_mul_quant(gu[:, :inter], gu[:, inter:])
+    y = ext.w8a8_scaled_gemm(q, w, s, ws)
+    q2, s2 = ext.silu_mul_quant(gu[:, :inter], gu[:, inter:])
+    assert torch.equal(q, q2) and torch.equal(s, s2), "same input, same codes"
+    rows = torch.tensor([0, 1, 777, 4095, 4096, 8190, 8191] + list(range(3000, 3057)))
+    gu_s = gu[rows].cpu()
+    q_ref, s_ref = oracle.silu_mul_quant(gu_s[:, :inter], gu_s[:, inter:])
+    assert torch.equal(q[rows].cpu(), q_ref) and torch.equal(s[rows].cpu(), s_ref)
+    cols = slice(7168 - 96, 7168)
+    ref = oracle.w8a8_gemm(q_ref, w[cols].cpu(), s_ref.view(-1), ws[cols].cpu())
+    assert torch.equal(y[rows][:, cols].cpu().contiguous().view(torch.int16), ref.view(torch.int16))

@@ -204,3 +204,42 @@ def test_moe_topk_matches_oracle(cabi, ext, t, e, k):
     tv, ti = torch.topk(logits[1:], k, dim=-1)
     assert torch.equal(ids_ref[1:].long(), ti)
     assert torch.allclose(w_ref[1:], torch.softmax(tv, dim=-1), rtol=1e-5, atol=1e-8)
+
+
+def test_moe_full_size_sampled_experts_match_oracle():
+    # the configuration's full size (4096 tokens, 256 experts of 4096 x 7168 + 7168 x 2048, top-8,
+    # group-128 activation scales) on the device; the oracle re-derives every stage for a few
+    # experts (their routed rows only) and the combined output for the tokens those experts serve
+    from bw1000_dsv4_kernels_b200 import moe
+    dev = torch.device("cuda")
+    t, h, e, inter, topk = wl.MOE_TOKENS, wl.HIDDEN, wl.MOE_EXPERTS, wl.MOE_INTER, wl.MOE_TOPK
+    inp = wl.moe_inputs(t, h, e, inter, topk, device=dev, seed=0)
+    layer = moe.W8A8MoE(inp.w13, inp.w13_scale, inp.w2, inp.w2_scale, e, group_scaled=True)
+    out = layer.forward(inp.x, inp.topk_ids, inp.topk_w, keep_trace=True)
+    tr = layer.last_trace
+    torch.cuda.synchronize()
+    # front end against the oracle on the whole problem (cheap)
+    q_ref, s_ref = oracle.per_token_group_quant_int8(inp.x.cpu(), 128)
+    off_ref, src_ref, dst_ref = oracle.moe_segments(inp.topk_ids.cpu(), e)
+    assert int(off_ref[-1]) == t * topk
+    assert torch.equal(tr.offsets.cpu(), off_ref) and torch.equal(tr.dst_slot.cpu(), dst_ref)
+    assert torch.equal(tr.src_row.cpu(), src_ref)
+    assert torch.equal(tr.a_q.cpu(), q_ref[src_ref.long()]) and torch.equal(tr.a_s.cpu(), s_ref[src_ref.long()])
+    rows = (off_ref[1:] - off_ref[:-1])
+    picks = [int(rows.argmax()), int(rows.argmin()), 123]          # the fullest, the emptiest, one more
+    z_dev = tr.z.cpu()
+    for ex in picks:
+        lo, hi = int(off_ref[ex]), int(off_ref[ex + 1])
+        if hi == lo:
+            continue
+        one = torch.tensor([0, hi - lo], dtype=torch.int32)
+        a_q, a_s = q_ref[src_ref[lo:hi].long()], s_ref[src_ref[lo:hi].long()]
+        y = oracle.grouped_gemm(a_q, inp.w13[ex:ex + 1].cpu(), a_s, inp.w13_scale[ex:ex + 1].cpu(), one)
+        assert torch.equal(tr.y[lo:hi].cpu().view(torch.int16), y.view(torch.int16)), f"gate/up GEMM, expert {ex}"
+        h_q, h_s = oracle.silu_mul_quant(y[:, :inter], y[:, inter:])
+        assert torch.equal(tr.h_q[lo:hi].cpu(), h_q) and torch.equal(tr.h_s[lo:hi].cpu(), h_s), f"silu, expert {ex}"
+        z = oracle.grouped_gemm(h_q, inp.w2[ex:ex + 1].cpu(), h_s.view(-1), inp.w2_scale[ex:ex + 1].cpu(), one)
+        assert torch.equal(z_dev[lo:hi].view(torch.int16), z.view(torch.int16)), f"down GEMM, expert {ex}"
+    # combine: the oracle on the device's z (verified above for the sampled experts) for every token
+    ref = oracle.moe_combine(z_dev, dst_ref, inp.topk_w.cpu())
+    assert torch.equal(out.cpu().view(torch.int16), ref.view(torch.int16)), "combined output"
