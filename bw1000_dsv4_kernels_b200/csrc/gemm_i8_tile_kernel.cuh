@@ -154,7 +154,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             ptx::tc_fence_after_sync();
             const int row = c.a_row0 + quarter * 32 + lane;
             const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-            drain_accumulator<BN>(p, t_lane, sbs, row, row < c.row_end, c.n0, vec_ok);
+            // a warp whose 32 rows all lie past the end of the segment has nothing to load or store
+            if (c.a_row0 + quarter * 32 < c.row_end)
+                drain_accumulator<BN>(p, t_lane, sbs, row, row < c.row_end, c.n0, vec_ok);
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(acc_empty_bar(acc));
