@@ -49,6 +49,19 @@ def test_abi_version_and_argument_errors_without_a_device():
     assert lib.launch_grouped_gemm(one, one, one, one, null, one, 4, 2, 8, 32, 1, null) == 1
     assert lib.launch_moe_segments(null, 4, 2, 8, 0, null, null, null, null) == 1
     assert lib.launch_gather_rows(one, one, one, 4, 24, null, null, 0, null, null) == 1
+    # additions without a reference counterpart: same argument discipline
+    assert lib.launch_silu_mul_strided(one, ctypes.c_longlong(4), one, ctypes.c_longlong(8), one, 2, 8, null) == 1
+    assert b"stride" in lib.dsv4_last_error()
+    assert lib.launch_moe_combine_exchange(null, null, null, null, null, 2, 4, 0, 4, 2, 64, null) == 1
+    assert lib.launch_moe_combine_exchange(null, null, null, null, null, 2, 4, 4, 4, 2, 64, null) == 0   # no tokens
+    ptrs = (ctypes.c_void_p * 9)(*([16] * 9))
+    assert lib.launch_moe_combine_exchange(ptrs, ptrs, one, one, ptrs, 9, 4, 0, 4, 2, 64, null) == 1     # > 8 ranks
+    # the overlap option is a process-wide switch, off by default
+    assert lib.dsv4_get_overlap_previous_kernel() == 0
+    lib.dsv4_set_overlap_previous_kernel(1)
+    assert lib.dsv4_get_overlap_previous_kernel() == 1
+    lib.dsv4_set_overlap_previous_kernel(0)
+    assert lib.dsv4_get_overlap_previous_kernel() == 0
 
 
 def test_operator_module_lists_the_reference_names():
@@ -56,5 +69,6 @@ def test_operator_module_lists_the_reference_names():
     for name in ("per_token_quant_int8", "rmsnorm", "silu_and_mul", "silu_mul_quant", "add_rmsnorm_quant",
                  "w8a8_scaled_gemm"):
         assert hasattr(ext, name) and hasattr(ext, name + "_stream")      # dsv4_native_ext.cpp:429-442
-    for name in ("w8a8_gemm", "per_token_group_quant_int8", "grouped_gemm", "moe_segments", "moe_combine"):
+    for name in ("w8a8_gemm", "per_token_group_quant_int8", "grouped_gemm", "moe_segments", "moe_combine", "moe_topk",
+                 "moe_combine_exchange", "gather_rows", "w8a8_gemm_allgather", "set_overlap_previous_kernel"):
         assert hasattr(ext, name)

@@ -101,6 +101,11 @@ def test_shard_ranges_and_seeded_shards_are_consistent():
     assert [moe.expert_range(r, 8, 256) for r in range(8)][-1] == (224, 256)
     with pytest.raises(AssertionError):
         tp_linear.column_range(0, 3, 28672 + 1)
+    # token ownership of the fused combine: contiguous blocks that cover every token exactly once
+    for tokens, world in ((4096, 8), (4099, 8), (7, 8), (1, 2), (0, 4)):
+        ranges = [moe.token_range(r, world, tokens) for r in range(world)]
+        assert ranges[0][0] == 0 and ranges[-1][1] == tokens
+        assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:])) and all(lo <= hi for lo, hi in ranges)
     full = wl.tp_linear_inputs(0, 1, m=4, k=64, n=512, slab=64, seed=1)
     parts = [wl.tp_linear_inputs(r, 4, m=4, k=64, n=512, slab=64, seed=1) for r in range(4)]
     assert torch.equal(torch.cat([p.w for p in parts]), full.w)
