@@ -88,6 +88,21 @@ def test_moe_combine_matches_oracle(cabi, ext, out_f32):
         assert torch.equal(out2.cpu().view(torch.int16), ref.view(torch.int16))
 
 
+@pytest.mark.parametrize("t,topk,h,e", [(33, 12, 2304, 16), (5, 1, 8, 4), (9, 17, 7168, 32)])
+def test_moe_combine_many_slots_and_wide_rows(cabi, t, topk, h, e):
+    # more than eight slots per token (two batches of row pointers) and rows wider than one pass
+    ids, w = wl.moe_routing(t, e, topk, seed=t + topk)
+    _, _, dst = oracle.moe_segments(ids, e - e // 4, 0)   # a quarter of the experts elsewhere: some slots are -1
+    z = wl.randn_bf16((t * topk, h), seed=8)
+    for out_f32 in (False, True):
+        ref = oracle.moe_combine(z, dst, w, out_f32)
+        out = cabi.moe_combine(z.cuda(), dst.cuda(), w.cuda(), out_f32).cpu()
+        if out_f32:
+            assert torch.equal(out, ref)
+        else:
+            assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
+
+
 def _oracle_moe(inp, e, lo, hi, group_scaled, out_f32):
     """The MoE chain with every step taken from the oracle."""
     inter = inp.w2.shape[2]
