@@ -28,6 +28,17 @@ def _entry(us, peaks, bytes_=None, ops=None, us_host_loop=None):
     return out
 
 
+def _hold(fn, n):
+    """fn with its last n results kept alive, so that the outputs rotate through as many buffers as
+    the inputs do (a freed output would be handed out again at once and stay in L2)."""
+    keep = [None] * max(1, n)
+
+    def call(i):
+        keep[i % len(keep)] = fn(i)
+
+    return call
+
+
 def _iters(us_guess):
     return int(max(10, min(200, 20000 / max(us_guess, 1.0))))
 
@@ -49,7 +60,7 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launch
         nb = m * K * 2
         n = rotation_count(nb * 3 // 2)
         xs = [wl.activations_with_outliers(m, K, device=dev, seed=i) for i in range(n)]
-        us, lp = both(lambda i: ext.per_token_quant_int8(xs[i % n]))
+        us, lp = both(_hold(lambda i: ext.per_token_quant_int8(xs[i % n]), n))
         sec[f"M={m}"] = _entry(us, peaks, bytes_=3 * m * K + 4 * m, us_host_loop=lp)
         del xs
     res["per_token_quant_int8 K=7168"] = sec
@@ -59,7 +70,7 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launch
     for m in (4096,):
         n = rotation_count(m * K * 3)
         xs = [wl.randn_bf16((m, K), device=dev, seed=i) for i in range(n)]
-        us, lp = both(lambda i: ext.per_token_group_quant_int8(xs[i % n], 128))
+        us, lp = both(_hold(lambda i: ext.per_token_group_quant_int8(xs[i % n], 128), n))
         sec[f"M={m}"] = _entry(us, peaks, bytes_=3 * m * K + 4 * m * (K // 128), us_host_loop=lp)
         del xs
     res["per_token_group_quant_int8 K=7168 gs=128"] = sec
@@ -76,7 +87,7 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launch
         n = min(n, 48)
         xs = [wl.randn_bf16((m, K), device=dev, seed=i) for i in range(n)]
         rs = [wl.randn_bf16((m, K), device=dev, seed=100 + i) for i in range(n)]
-        us, lp = both(lambda i: ext.add_rmsnorm_quant(rs[i % n], xs[i % n], gamma, 1e-6))
+        us, lp = both(_hold(lambda i: ext.add_rmsnorm_quant(rs[i % n], xs[i % n], gamma, 1e-6), n))
         quant_sec[f"M={m}"] = _entry(us, peaks, bytes_=m * (7 * K + 4) + 2 * K, us_host_loop=lp)
         qs = [ext.add_rmsnorm_quant(rs[i], xs[i], gamma, 1e-6) for i in range(min(n, 5))]
         nq = len(qs)
@@ -132,7 +143,7 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launch
         nb = m * 2 * I * 2
         n = max(2, min(rotation_count(nb), 24)) if m < 8192 else 2
         gus = [wl.randn_bf16((m, 2 * I), device=dev, seed=i) for i in range(n)]
-        us, lp = both(lambda i: ext.silu_mul_quant(gus[i % n][:, :I], gus[i % n][:, I:]), _iters(100 if m > 64 else 5))
+        us, lp = both(_hold(lambda i: ext.silu_mul_quant(gus[i % n][:, :I], gus[i % n][:, I:]), n), _iters(100 if m > 64 else 5))
         silu_sec[f"M={m}"] = _entry(us, peaks, bytes_=m * (5 * I + 4), us_host_loop=lp)
         q, s = ext.silu_mul_quant(gus[0][:, :I], gus[0][:, I:])
         del gus
