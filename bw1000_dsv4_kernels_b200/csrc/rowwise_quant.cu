@@ -862,18 +862,18 @@ int ptgq(const void* x, void* q, void* s, int M, int K, int gs, cudaStream_t st)
     auto xv = static_cast<const uint4*>(x);
     auto qv = static_cast<uint2*>(q);
     auto sp = static_cast<float*>(s);
-    const int64_t want = (nvec + 256 * 2 - 1) / (256 * 2);
+    const int64_t want = (nvec + 256 * 4 - 1) / (256 * 4);
     const int grid = (int)(want < 1 ? 1 : (want > (1 << 20) ? (1 << 20) : want));
     bool done = false;
     if (vec) {
         done = true;
         switch (lpg) {
-            case 1: ptgq_vec_kernel<1, 2><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
-            case 2: ptgq_vec_kernel<2, 2><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
-            case 4: ptgq_vec_kernel<4, 2><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
-            case 8: ptgq_vec_kernel<8, 2><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
-            case 16: ptgq_vec_kernel<16, 2><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
-            case 32: ptgq_vec_kernel<32, 2><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
+            case 1: ptgq_vec_kernel<1, 4><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
+            case 2: ptgq_vec_kernel<2, 4><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
+            case 4: ptgq_vec_kernel<4, 4><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
+            case 8: ptgq_vec_kernel<8, 4><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
+            case 16: ptgq_vec_kernel<16, 4><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
+            case 32: ptgq_vec_kernel<32, 4><<<grid, 256, 0, st>>>(xv, qv, sp, nvec); break;
             default: done = false;
         }
     }
