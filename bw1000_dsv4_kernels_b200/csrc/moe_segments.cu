@@ -380,36 +380,47 @@ __global__ void __launch_bounds__(128) moe_combine_exchange_kernel(ExchangeArgs 
     __shared__ const uint4* rowp[kBatch];
     __shared__ float wk[kBatch];
     const int V = H >> 3;
+    const bool one_batch = topk <= kBatch;      // the usual case: the row pointers are set up once per token
+    // expert id -> owning rank -> that rank's slot for this (token, j) -> address of the expert row
+    auto load_rows = [&](int t, int j0) {
+        if (threadIdx.x < kBatch) {
+            const int j = j0 + threadIdx.x;
+            const uint4* ptr = nullptr;
+            float wj = 0.0f;
+            if (j < topk) {
+                const int64_t pair = (int64_t)t * topk + j;
+                const int e = __ldg(ids + pair);
+                const int rank = e >= 0 ? e / experts_per_rank : G;
+                wj = __ldg(w + pair);
+#pragma unroll
+                for (int r = 0; r < kMaxRanks; ++r) {
+                    if (r == rank && r < G) {
+                        const int slot = a.slot[r][pair];
+                        if (slot >= 0) ptr = reinterpret_cast<const uint4*>(a.z[r] + (int64_t)slot * H);
+                    }
+                }
+            }
+            rowp[threadIdx.x] = ptr;
+            wk[threadIdx.x] = wj;
+        }
+    };
     for (int t = t0 + blockIdx.x; t < t1; t += gridDim.x) {
         float acc[4][8];                        // up to four 16-byte vectors per thread and pass
+        if (one_batch) {
+            load_rows(t, 0);
+            __syncthreads();
+        }
         for (int vb = 0; vb < V; vb += 4 * 128) {
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
                 for (int e = 0; e < 8; ++e) acc[i][e] = 0.0f;
             for (int j0 = 0; j0 < topk; j0 += kBatch) {
-                __syncthreads();                // the previous batch's pointers have been used
-                if (threadIdx.x < kBatch) {
-                    const int j = j0 + threadIdx.x;
-                    const uint4* ptr = nullptr;
-                    float wj = 0.0f;
-                    if (j < topk) {
-                        const int64_t pair = (int64_t)t * topk + j;
-                        const int e = __ldg(ids + pair);
-                        const int rank = e >= 0 ? e / experts_per_rank : G;
-                        wj = __ldg(w + pair);
-#pragma unroll
-                        for (int r = 0; r < kMaxRanks; ++r) {
-                            if (r == rank && r < G) {
-                                const int slot = a.slot[r][pair];
-                                if (slot >= 0) ptr = reinterpret_cast<const uint4*>(a.z[r] + (int64_t)slot * H);
-                            }
-                        }
-                    }
-                    rowp[threadIdx.x] = ptr;
-                    wk[threadIdx.x] = wj;
+                if (!one_batch) {
+                    __syncthreads();            // the previous batch's pointers have been used
+                    load_rows(t, j0);
+                    __syncthreads();
                 }
-                __syncthreads();
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int v = vb + i * 128 + threadIdx.x;
