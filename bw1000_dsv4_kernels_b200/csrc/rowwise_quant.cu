@@ -257,6 +257,8 @@ __global__ void __launch_bounds__(kSumLanes) add_rmsnorm_quant_vec_kernel(
     __shared__ float red_max[32];
     const int V = K >> 3, tid = threadIdx.x;
     const uint64_t once = l2_evict_first_policy();  // x and the residual pass through L2 once
+    // 1.0f that the compiler cannot see through (K is positive): see quant_rn_lowbyte2
+    const float2 one2 = splat2(__int_as_float(0x3f800000 | (K >> 31)));
     for (int row = blockIdx.x; row < M; row += gridDim.x) {
         uint4* rr = reinterpret_cast<uint4*>(res + (int64_t)row * K);
         const uint4* xr = reinterpret_cast<const uint4*>(x + (int64_t)row * K);
@@ -273,52 +275,63 @@ __global__ void __launch_bounds__(kSumLanes) add_rmsnorm_quant_vec_kernel(
                 xv[i] = make_uint4(0, 0, 0, 0);
             }
         }
-        float a[VPT][8];
+        // Two elements per instruction where the order of operations allows it (packed f32x2: each half
+        // is an independent, correctly rounded operation); the lane's sum of squares stays a sequential
+        // chain of separately rounded adds in element order.
+        float2 a[VPT][4];
         float ss = 0.0f;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            float r8[8], x8[8];
-            unpack8(rv[i], r8);
-            unpack8(xv[i], x8);
+            const uint32_t rw[4] = {rv[i].x, rv[i].y, rv[i].z, rv[i].w}, xw[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w};
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                a[i][e] = __fadd_rn(r8[e], x8[e]);
-                ss = __fadd_rn(ss, __fmul_rn(a[i][e], a[i][e]));
+            for (int e = 0; e < 4; ++e) {
+                a[i][e] = __fadd2_rn(bf16x2_to_f32x2(rw[e]), bf16x2_to_f32x2(xw[e]));
+                const float2 sq = __fmul2_rn(a[i][e], a[i][e]);
+                ss = __fadd_rn(ss, sq.x);
+                ss = __fadd_rn(ss, sq.y);
             }
             const int idx = tid + i * kSumLanes;
             if (idx < V) {
                 uint4 o;
-                o.x = pack_bf16x2_rn(a[i][0], a[i][1]);
-                o.y = pack_bf16x2_rn(a[i][2], a[i][3]);
-                o.z = pack_bf16x2_rn(a[i][4], a[i][5]);
-                o.w = pack_bf16x2_rn(a[i][6], a[i][7]);
+                o.x = pack_bf16x2_rn(a[i][0].x, a[i][0].y);
+                o.y = pack_bf16x2_rn(a[i][1].x, a[i][1].y);
+                o.z = pack_bf16x2_rn(a[i][2].x, a[i][2].y);
+                o.w = pack_bf16x2_rn(a[i][3].x, a[i][3].y);
                 st_once(rr + idx, o, once);
             }
         }
         const float total = block_sum_256(ss, red_sum);
         const float rrms = rrms_from_sumsq(total, K, eps);
+        const float2 rrms2 = splat2(rrms);
         float am = 0.0f;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int idx = tid + i * kSumLanes;
-            float w8[8];
             const uint4 wv = (idx < V) ? __ldg(wr + idx) : make_uint4(0, 0, 0, 0);
-            unpack8(wv, w8);
+            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                a[i][e] = __fmul_rn(__fmul_rn(a[i][e], rrms), w8[e]);
-                am = fmaxf(am, fabsf(a[i][e]));
+            for (int e = 0; e < 4; ++e) {
+                a[i][e] = __fmul2_rn(__fmul2_rn(a[i][e], rrms2), bf16x2_to_f32x2(ww[e]));
+                am = max3_abs(am, a[i][e].x, a[i][e].y);
             }
         }
         am = block_max(am, red_max);
         float scale, inv;
         scale_from_amax(am, scale, inv);
         if (tid == 0) s[row] = scale;
+        const float2 inv2 = splat2(inv);
         uint2* qr = reinterpret_cast<uint2*>(q + (int64_t)row * K);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int idx = tid + i * kSumLanes;
-            if (idx < V) qr[idx] = quant8_rn(a[i], inv);
+            if (idx < V) {
+                const float2 c0 = quant_rn_lowbyte2(a[i][0], inv2, one2), c1 = quant_rn_lowbyte2(a[i][1], inv2, one2);
+                const float2 c2 = quant_rn_lowbyte2(a[i][2], inv2, one2), c3 = quant_rn_lowbyte2(a[i][3], inv2, one2);
+                uint2 o;
+                o.x = pack_lowbytes(__float_as_uint(c0.x), __float_as_uint(c0.y), __float_as_uint(c1.x), __float_as_uint(c1.y));
+                o.y = pack_lowbytes(__float_as_uint(c2.x), __float_as_uint(c2.y), __float_as_uint(c3.x), __float_as_uint(c3.y));
+                qr[idx] = o;
+            }
         }
         __syncthreads();
     }
