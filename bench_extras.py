@@ -7,7 +7,7 @@ wherever one set is smaller than L2, so HBM-bound numbers are not L2 numbers.
 """
 import torch
 
-from . import workloads as wl
+from tests import workloads as wl
 
 HBM = "hbm"
 TENSOR = "tensor"
@@ -43,7 +43,7 @@ def _iters(us_guess):
     return int(max(10, min(200, 20000 / max(us_guess, 1.0))))
 
 
-def run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launches_graph):
+def run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launches_graph, timer=None):
     res = {"timing": "us = per-launch device time from CUDA-graph replays of 20 launches over rotating buffers; "
                      "us_host_loop = per-call time when launched one by one from Python"}
 
@@ -100,7 +100,7 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launch
     # the dependent chain at decode sizes, strictly serialised and with the GEMM allowed to overlap
     # the quantiser before it (set-up and weight loads start early; see set_overlap_previous_kernel)
     chain_sec = {}
-    for m in (1, 16, 64, 256):
+    for m in (1, 16, 64, 256, 2048):
         n = 6
         xs = [wl.randn_bf16((m, K), device=dev, seed=i) for i in range(n)]
         rs = [wl.randn_bf16((m, K), device=dev, seed=100 + i) for i in range(n)]
@@ -157,73 +157,107 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launch
     torch.cuda.empty_cache()
 
     try:
-        res["moe_ffn T=4096 E=256 I=2048 top8"] = _moe_section(ext, dev, rank, world, peaks, time_launches, time_launches_graph)
+        res["moe_ffn T=4096 E=256 I=2048 top8"] = _moe_section(ext, dev, rank, world, peaks, timer, time_launches_graph)
     except Exception as exc:  # pragma: no cover
         res["moe_ffn"] = {"error": f"{type(exc).__name__}: {exc}"}
-    torch.cuda.empty_cache()
-    try:
-        res["tp_linear M=8192 K=7168 N=28672"] = _tp_section(ext, dev, rank, world, peaks, time_launches)
-    except Exception as exc:  # pragma: no cover
-        res["tp_linear"] = {"error": f"{type(exc).__name__}: {exc}"}
     torch.cuda.empty_cache()
     return res
 
 
-def _max_over_ranks(ms, dev, world):
-    if world == 1:
-        return ms
-    import torch.distributed as dist
-    t = torch.tensor([ms], device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
+def _moe_reference_rows(ext, tokens, x, topk_ids, topk_w, dev, group_scaled):
+    """The single-GPU chain for a few tokens, recomputed on this device with one launch per routed
+    (token, expert) pair: the expert's weights are regenerated from their seed, the token goes
+    through quantiser -> gate/up GEMM -> silu_mul_quant -> down GEMM as a one-row batch, and the
+    token's rows are summed by moe_combine in slot order.  Different launch shapes from the layer
+    (one row, one expert), same arithmetic: the result must equal the layer's rows bit for bit."""
+    H, I, topk = wl.HIDDEN, wl.MOE_INTER, wl.MOE_TOPK
+    rows = []
+    off = torch.tensor([0, 1], dtype=torch.int32, device=dev)
+    for t in tokens:
+        xt = x[t:t + 1].contiguous()
+        if group_scaled:
+            q, s = ext.per_token_group_quant_int8(xt, 128)
+        else:
+            q, s = ext.per_token_quant_int8(xt)
+        zs = []
+        for j in range(topk):
+            e = int(topk_ids[t, j])
+            base = 1000 + 4 * e
+            w13 = wl.int8_weights((2 * I, H), dev, base).unsqueeze(0)      # the seeds moe_inputs gives expert e
+            w2 = wl.int8_weights((H, I), dev, base + 1).unsqueeze(0)
+            s13 = wl.channel_scales((2 * I,), dev, base + 2).unsqueeze(0)
+            s2 = wl.channel_scales((H,), dev, base + 3).unsqueeze(0)
+            y = ext.grouped_gemm(q, w13, s, s13, off)
+            hq, hs = ext.silu_mul_quant(y[:, :I], y[:, I:])
+            zs.append(ext.grouped_gemm(hq, w2, hs, s2, off))
+        z = torch.cat(zs)
+        slot = torch.arange(topk, dtype=torch.int32, device=dev).view(1, topk)
+        rows.append(ext.moe_combine(z, slot.contiguous(), topk_w[t:t + 1].contiguous(), False))
+    return torch.cat(rows)
 
 
-def _sync(world):
-    if world > 1:
-        import torch.distributed as dist
-        dist.barrier()
-    torch.cuda.synchronize()
-
-
-def _moe_section(ext, dev, rank, world, peaks, time_launches, time_launches_graph=None):
+def _moe_section(ext, dev, rank, world, peaks, timer, time_launches_graph):
     """MoE FFN, experts sharded over the ranks (expert parallel), tokens and routing replicated.
-    Weight-bandwidth-bound: ~128 routed rows per expert against 44 MB of int8 weights per expert."""
-    from . import moe
+    Weight-bandwidth-bound: ~128 routed rows per expert against 44 MB of int8 weights per expert.
+    Times are medians over repeats of 10 forward calls, max over ranks per repeat."""
+    from bw1000_dsv4_kernels_b200 import moe
     T, H, E, I, topk = wl.MOE_TOKENS, wl.HIDDEN, wl.MOE_EXPERTS, wl.MOE_INTER, wl.MOE_TOPK
     lo, hi = moe.expert_range(rank, world, E)
     inp = wl.moe_inputs(T, H, E, I, topk, device=dev, seed=0, expert_lo=lo, expert_hi=hi)
     out = {}
+    K_CALLS, REPEATS = 10, 7
+
+    def med(fn):
+        t = timer.run(fn, K_CALLS, REPEATS, warmup=2)
+        return {"ms": round(t["ms_per_step"], 4), "ms_min": round(t["ms_per_step_min"], 4), "ms_max": round(t["ms_per_step_max"], 4)}
+
     for name, gs in (("group_scaled", True), ("per_token", False)):
         layer = moe.W8A8MoE(inp.w13, inp.w13_scale, inp.w2, inp.w2_scale, E, expert_lo=lo, group_scaled=gs)
-        fwd = lambda i: layer.forward(inp.x, inp.topk_ids, inp.topk_w)
-        part = lambda i: layer.local_partial(inp.x, inp.topk_ids, inp.topk_w, out_f32=(world > 1))
-        _sync(world)
-        ms_local = _max_over_ranks(time_launches(part, 10, warmup=2), dev, world)
-        _sync(world)
-        ms_full = _max_over_ranks(time_launches(fwd, 10, warmup=2), dev, world)
+        t_local = med(lambda i: layer.local_partial(inp.x, inp.topk_ids, inp.topk_w, out_f32=(world > 1)))
         rows_total = T * topk
         ops = 2.0 * rows_total * (2 * I * H + H * I)
         w_bytes = (hi - lo) * (2 * I * H + H * I)
-        out[name] = {
-            "ms_local_experts": round(ms_local, 4), "ms_with_allreduce": round(ms_full, 4),
-            "TOPS_whole_job": round(ops / (ms_full * 1e-3) / 1e12, 1),
-            "weight_GBps_per_rank": round(w_bytes / (ms_local * 1e-3) / 1e9, 1),
-            "weight_hbm_frac": round(w_bytes / (ms_local * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+        sec = {
+            "local_experts": t_local,
+            "weight_GBps_per_rank": round(w_bytes / (t_local["ms"] * 1e-3) / 1e9, 1),
+            "weight_hbm_frac": round(w_bytes / (t_local["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
             "experts_per_rank": hi - lo, "ranks": world,
         }
-        if world > 1:
-            # combine fused with the exchange over peer memory instead of fp32 partials + all-reduce
+        if world == 1:
+            sec["TOPS_whole_job"] = round(ops / (t_local["ms"] * 1e-3) / 1e12, 1)
+            y = layer.forward(inp.x, inp.topk_ids, inp.topk_w)
+        else:
+            t_ar = med(lambda i: layer.forward(inp.x, inp.topk_ids, inp.topk_w))
+            sec["with_nccl_allreduce"] = t_ar
+            y = None
             try:
+                # combine fused with the exchange over peer memory instead of fp32 partials + all-reduce
                 ex = moe.ExchangeW8A8MoE(inp.w13, inp.w13_scale, inp.w2, inp.w2_scale, E, rank, world, t_max=T,
                                          topk=topk, device=dev, group_scaled=gs)
-                _sync(world)
-                ms_ex = _max_over_ranks(time_launches(lambda i: ex.forward(inp.x, inp.topk_ids, inp.topk_w), 10, warmup=2),
-                                        dev, world)
-                out[name]["ms_with_fused_exchange"] = round(ms_ex, 4)
-                out[name]["TOPS_whole_job_fused_exchange"] = round(ops / (ms_ex * 1e-3) / 1e12, 1)
+                t_ex = med(lambda i: ex.forward(inp.x, inp.topk_ids, inp.topk_w))
+                sec["with_fused_exchange"] = t_ex
+                sec["TOPS_whole_job"] = round(ops / (t_ex["ms"] * 1e-3) / 1e12, 1)
+                y = ex.forward(inp.x, inp.topk_ids, inp.topk_w).clone()
                 del ex
             except Exception as exc:  # pragma: no cover
-                out[name]["fused_exchange_error"] = f"{type(exc).__name__}: {exc}"
+                sec["fused_exchange_error"] = f"{type(exc).__name__}: {exc}"
+                sec["TOPS_whole_job"] = round(ops / (t_ar["ms"] * 1e-3) / 1e12, 1)
+        if y is not None:
+            # parity inside the run: a few of this rank's tokens against the one-GPU chain recomputed here
+            t0, t1 = moe.token_range(rank, world, T)
+            tokens = [t0, (t0 + t1) // 2, t1 - 1]
+            ref = _moe_reference_rows(ext, tokens, inp.x, inp.topk_ids, inp.topk_w, dev, gs)
+            torch.cuda.synchronize()
+            ok = bool(torch.equal(y[tokens].contiguous().view(torch.int16), ref.view(torch.int16)))
+            if world > 1:
+                import torch.distributed as dist
+                f = torch.tensor([1 if ok else 0], device=dev)
+                dist.all_reduce(f, op=dist.ReduceOp.MIN)
+                ok = bool(int(f.item()))
+            sec["parity_ok"] = ok
+            sec["parity"] = "3 tokens per rank recomputed with one-row launches from regenerated expert weights, bit for bit"
+        out[name] = sec
+        del layer
     # stage breakdown of the group-scaled chain on this rank
     layer = moe.W8A8MoE(inp.w13, inp.w13_scale, inp.w2, inp.w2_scale, E, expert_lo=lo, group_scaled=True)
     layer.local_partial(inp.x, inp.topk_ids, inp.topk_w, out_f32=False, keep_trace=True)
@@ -241,55 +275,5 @@ def _moe_section(ext, dev, rank, world, peaks, time_launches, time_launches_grap
         "grouped_gemm down": lambda i: ext.grouped_gemm(tr.h_q, inp.w2, tr.h_s, inp.w2_scale, tr.offsets),
         "moe_combine": lambda i: ext.moe_combine(tr.z, tr.dst_slot, inp.topk_w, False),
     }
-    if time_launches_graph is not None:   # device time per launch from CUDA-graph replays
-        out["stages_us_rank0"] = {k: round(1e3 * time_launches_graph(f, 10, 5), 1) for k, f in stages.items()}
-    else:
-        out["stages_us_rank0"] = {k: round(1e3 * time_launches(f, 10, warmup=2), 1) for k, f in stages.items()}
-    return out
-
-
-def _tp_section(ext, dev, rank, world, peaks, time_launches):
-    """Column-sharded linear: quantise (replicated) + GEMM on N/G columns + NCCL all-gather."""
-    from . import tp_linear
-    M, K, N = wl.TP_M, wl.HIDDEN, wl.TP_N
-    inp = wl.tp_linear_inputs(rank, world, m=M, k=K, n=N, device=dev, seed=0)
-    layer = tp_linear.ColumnParallelW8A8Linear(inp.w, inp.w_scale, rank, world)
-    q, s = ext.per_token_quant_int8(inp.x)
-    _sync(world)
-    ms_gemm = _max_over_ranks(time_launches(lambda i: ext.w8a8_scaled_gemm(q, inp.w, s, inp.w_scale), 10, warmup=3), dev, world)
-    _sync(world)
-    ms_local = _max_over_ranks(time_launches(lambda i: layer.local_gemm(inp.x), 10, warmup=3), dev, world)
-    _sync(world)
-    ms_slabs = _max_over_ranks(time_launches(lambda i: layer.forward_slabs(inp.x), 10, warmup=3), dev, world)
-    ops = 2.0 * M * N * K
-    n_local = N // world
-    out = {
-        "ranks": world, "columns_per_rank": n_local,
-        "gemm_only_ms": round(ms_gemm, 4), "gemm_only_TOPS_whole_job": round(ops / (ms_gemm * 1e-3) / 1e12, 1),
-        "gemm_tensor_frac_per_rank": round(ops / world / (ms_gemm * 1e-3) / 1e12 / (2.0 * peaks["bf16_tflops"]), 4),
-        "quant_plus_gemm_ms": round(ms_local, 4),
-        "quant_gemm_allgather_ms": round(ms_slabs, 4),
-        "quant_gemm_allgather_TOPS_whole_job": round(ops / (ms_slabs * 1e-3) / 1e12, 1),
-    }
-    if world > 1:
-        try:
-            fused = tp_linear.FusedColumnParallelW8A8Linear(inp.w, inp.w_scale, rank, world, m_max=M, device=dev)
-            _sync(world)
-            ms_fused = _max_over_ranks(time_launches(lambda i: fused.forward(inp.x), 10, warmup=3), dev, world)
-            out["fused_quant_gemm_allgather_ms"] = round(ms_fused, 4)
-            out["fused_TOPS_whole_job"] = round(ops / (ms_fused * 1e-3) / 1e12, 1)
-            out["fused_note"] = ("one kernel: the GEMM's tile epilogue stages each bf16 tile in shared memory and sends it "
-                                 "with TMA tile stores to every rank's row-major [M,N] buffer (symmetric memory, over "
-                                 "NVLink), between two symmetric-memory barriers; includes the quantiser")
-            sent = (world - 1) * M * n_local * 2
-            out["fused_nvlink_GBps_sent_per_rank"] = round(sent / (ms_fused * 1e-3) / 1e9, 1)
-            out["fused_nvlink_frac_of_770"] = round(sent / (ms_fused * 1e-3) / 1e9 / 770.0, 4)
-            del fused
-        except Exception as exc:  # pragma: no cover
-            out["fused_error"] = f"{type(exc).__name__}: {exc}"
-        recv = (world - 1) * M * n_local * 2
-        ag_ms = max(ms_slabs - ms_local, 1e-6)
-        out["allgather_bytes_received_per_rank"] = recv
-        out["allgather_GBps_per_rank_if_not_overlapped"] = round(recv / (ag_ms * 1e-3) / 1e9, 1)
-        out["nvlink_note"] = "measured peer copy on this pool: 770 GB/s per direction per GPU"
+    out["stages_us_rank0"] = {k: round(1e3 * time_launches_graph(f, 10, 7), 1) for k, f in stages.items()}
     return out

@@ -147,6 +147,22 @@ int launch_w8a8_gemm(const void* A, const void* B, const void* sa, const void* s
     return gemm_i8(a, cs(stream));
 }
 
+// Test hook, deliberately not declared in include/dsv4_w8a8.h: the same launch as launch_w8a8_gemm (or
+// launch_grouped_gemm when expert_offsets is not null), except that the kernel's producer issues no tile
+// loads and every bounded wait gives up after wait_limit_ns.  All consumer waits of the launch therefore
+// run out: the kernel must record the wait site in the device status word, leave through its normal
+// teardown (tensor memory freed) and return; nothing is written to C.  The launch itself returns 0.
+DSV4_API int dsv4_test_gemm_wait_expiry(const void* A, const void* B, const void* sa, const void* sb, void* C, int M,
+                                        int N, int K, const int* expert_offsets, int E,
+                                        unsigned long long wait_limit_ns, dsv4_stream_t stream) {
+    GemmArgs a{};
+    a.A = A; a.B = B; a.sa = static_cast<const float*>(sa); a.sb = static_cast<const float*>(sb); a.C = C;
+    a.offsets = expert_offsets; a.M = M; a.N = N; a.K = K; a.E = expert_offsets ? E : 1; a.sa_groups = 1; a.out_i32 = 0;
+    a.test_withhold_loads = 1;
+    a.test_wait_limit_ns = wait_limit_ns ? wait_limit_ns : 1000000ull;
+    return gemm_i8(a, cs(stream));
+}
+
 int launch_w8a8_gemm_v5(const void* A, const void* B, const void* sa, const void* sb, void* C, int M, int N,
                         int K, dsv4_stream_t stream) {
     return launch_w8a8_gemm(A, B, sa, sb, C, M, N, K, stream);

@@ -14,8 +14,11 @@
 
 namespace w8a8 {
 
-// Sticky per-device status word written by kernels whose bounded waits ran out.
+// Sticky per-device status word written by kernels whose bounded waits ran out, and the address of
+// its mirror in mapped host memory (set on the first GEMM launch on a device), which lets the next
+// launch see the failure without synchronising.
 __device__ int g_device_status = 0;
+__device__ int* g_host_status_mirror = nullptr;
 
 namespace {
 
@@ -46,6 +49,11 @@ struct Params {
     // slab of the other ranks' outputs, mapped into this process); same ldc.  npeers = 0: none.
     void* peerC[7];
     int npeers;
+    // every bounded wait of the launch gives up after this many nanoseconds
+    unsigned long long wait_limit_ns;
+    // test hook (never set through the public entry points): the producer issues no tile loads, so
+    // every consumer wait of the launch runs out and the kernel leaves through its give-up path
+    int withhold_loads;
 };
 
 template <int BN, int STAGES>
@@ -112,7 +120,7 @@ struct Scheduler {
             const int local = t - prefix[e] * tiles_n;
             const int nt = local / cnt, mt = local % cnt;
             c.a_row0 = p.offsets[e] + mt * BM;
-            c.row_end = p.offsets[e + 1];
+            c.row_end = min(p.offsets[e + 1], p.M);  // never past the end of C, whatever the list says
             c.n0 = nt * bn;
             c.b_row0 = e * p.N + c.n0;
             c.expert = e;
@@ -128,7 +136,7 @@ __device__ __forceinline__ void build_tile_prefix(const Params& p, int* prefix, 
     for (int e0 = 0; e0 < p.E; e0 += 32) {
         const int e = e0 + lane;
         int cnt = 0;
-        if (e < p.E) cnt = (p.offsets[e + 1] - p.offsets[e] + BM - 1) / BM;
+        if (e < p.E) cnt = max(0, (min(p.offsets[e + 1], p.M) - p.offsets[e] + BM - 1) / BM);  // a bad list gives no tiles
         int incl = cnt;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -142,7 +150,13 @@ __device__ __forceinline__ void build_tile_prefix(const Params& p, int* prefix, 
 }
 
 __device__ __forceinline__ void report_wait_failure(int site) {
-    atomicCAS(&g_device_status, 0, site);
+    if (atomicCAS(&g_device_status, 0, site) == 0) {
+        int* mirror = g_host_status_mirror;
+        if (mirror != nullptr) {
+            *reinterpret_cast<volatile int*>(mirror) = site;
+            __threadfence_system();
+        }
+    }
 }
 
 

@@ -26,9 +26,13 @@ struct PairSmem {
     static constexpr int kBBytes = 128 * BK;       // this CTA's 128 of the tile's 256 rows of B
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTilesBytes = STAGES * kStageBytes;
-    // output staging for the TMA-store epilogue: 4 slabs of [128 rows][64 bf16 = 128 B], 128B-swizzled
+    // output staging for the TMA-store epilogue: a ring of kOutSlots slabs of [128 rows][64 bf16 = 128 B],
+    // 128B-swizzled; a tile is four slabs, so the ring holds more than one tile's worth and the drain of
+    // a slab only waits for the stores of the slab kOutSlots back
+    static constexpr int kOutSlots = 5;
+    static constexpr int kOutSlabBytes = 128 * 128;
     static constexpr int kOutOff = kTilesBytes;
-    static constexpr int kOutBytes = TMA_STORE ? 4 * 128 * 128 : 0;
+    static constexpr int kOutBytes = TMA_STORE ? kOutSlots * kOutSlabBytes : 0;
     static constexpr int kSbOff = kOutOff + kOutBytes;          // 4 warps x 256 column scales
     static constexpr int kBarOff = kSbOff + 4 * 256 * 4;        // 8-byte aligned
     static constexpr int kNumBars = 2 * STAGES + 4;
@@ -102,7 +106,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
-        if (ptx::elect_one()) {
+        if (!p.withhold_loads && ptx::elect_one()) {
             // The first ring-full needs no free-stage wait; its B (weight) tiles are requested before the
             // dependency wait and its A tiles after it, so that a launch that overlaps the preceding
             // kernel (see set_overlap_previous_kernel) streams weights while that kernel still runs.
@@ -137,7 +141,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 const int a_row0 = (c.t % tiles_m) * 256 + (int)rank * 128;
                 const int b_row0 = (c.t / tiles_m) * PBN + (int)rank * 128;
                 for (; c.kb < k_blocks; ++c.kb) {
-                    if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u) || *abort_flag) {
+                    if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, p.wait_limit_ns) || *abort_flag) {
                         report_wait_failure(kWaitEmptyStage);
                         *abort_flag = 1;
                         c.t = total;  // leave both loops
@@ -167,7 +171,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t acc_phase = 0;
             bool ok = true;
             for (int t = pair; t < total && ok; t += npairs) {
-                if (!ptx::mbar_wait_bounded(acc_empty_bar(acc), acc_phase ^ 1u) || *abort_flag) {
+                if (!ptx::mbar_wait_bounded(acc_empty_bar(acc), acc_phase ^ 1u, p.wait_limit_ns) || *abort_flag) {
                     report_wait_failure(kWaitAccEmpty);
                     *abort_flag = 1;
                     break;
@@ -175,7 +179,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * PBN;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!ptx::mbar_wait_bounded(full_bar(stage), phase) || *abort_flag) {
+                    if (!ptx::mbar_wait_bounded(full_bar(stage), phase, p.wait_limit_ns) || *abort_flag) {
                         report_wait_failure(kWaitFullStage);
                         *abort_flag = 1;
                         ok = false;
@@ -205,6 +209,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         float* sbs = sb_tile + (warp - 2) * PBN;
         int acc = 0;
         uint32_t acc_phase = 0;
+        int out_slot = 0;  // next slab of the output staging ring (fused all-gather epilogue)
         const bool vec_ok = c_vector_stores_ok(p);
         for (int t = pair; t < total; t += npairs) {
             const int mt = t % tiles_m, nt = t / tiles_m;
@@ -214,7 +219,10 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 for (int j = lane; j < PBN; j += 32) sbs[j] = (n0 + j < p.N) ? __ldg(p.sb + n0 + j) : 0.0f;
             }
             __syncwarp();
-            if (!ptx::mbar_wait_bounded(acc_full_bar(acc), acc_phase) || *abort_flag) {
+            bool go = ptx::mbar_wait_bounded(acc_full_bar(acc), acc_phase, p.wait_limit_ns) && !*abort_flag;
+            // the epilogue below meets at named barriers, so its four warps leave together or not at all
+            if constexpr (TMA_STORE) go = ptx::barrier_and<2, kDrainThreads>(go);
+            if (!go) {
                 report_wait_failure(kWaitAccFull);
                 *abort_flag = 1;
                 break;
@@ -225,56 +233,61 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if constexpr (!TMA_STORE) {
                 drain_accumulator<PBN>(p, t_lane, sbs, row, row < p.M, n0, vec_ok);
             } else {
-                // Fused all-gather epilogue: the bf16 tile is staged in shared memory (four 64-column
-                // slabs, 128-byte swizzle so that the 16-byte stores of a quarter-warp hit all banks) and
-                // one thread sends it with TMA tile stores to this rank's buffer and to every peer's:
-                // full 128-byte rows per request over NVLink, no store instruction per destination.
-                const uint32_t out_base = tiles_base + L::kOutOff;
+                // Fused all-gather epilogue: the bf16 tile goes through shared memory one 64-column slab
+                // at a time (128-byte swizzle so that the 16-byte stores of a quarter-warp hit all banks)
+                // and one thread sends each slab with TMA tile stores to this rank's buffer and to every
+                // peer's: full 128-byte rows per request over NVLink, no store instruction per
+                // destination.  The slabs rotate through a ring of kOutSlots buffers, one bulk group per
+                // slab, so filling a slab waits only for the stores issued kOutSlots slabs earlier.
                 const int r = quarter * 32 + lane;  // row inside this CTA's 128-row half tile
                 const float sa = (row < p.M) ? __ldg(p.sa + row) : 0.0f;
-                if (warp == 2 && lane == 0) ptx::bulk_wait_group_read0();  // previous tile's stores have read the staging
-                asm volatile("bar.sync 2, %0;" ::"n"(kDrainThreads) : "memory");
+                const bool issuer = (warp == 2 && lane == 0);
 #pragma unroll 1
-                for (int cc = 0; cc < PBN / 32; ++cc) {
-                    uint32_t acc_r[32];
-                    __syncwarp();
-                    ptx::tmem_ld_32x32b_x32(t_lane + cc * 32, acc_r);
-                    ptx::tmem_ld_wait();
-                    const float4* sb4 = reinterpret_cast<const float4*>(sbs + cc * 32);
-                    uint32_t packed[16];
+                for (int sl = 0; sl < 4; ++sl) {
+                    const uint32_t slab = tiles_base + L::kOutOff + (uint32_t)out_slot * L::kOutSlabBytes;
+                    if (issuer) ptx::bulk_wait_group_read<L::kOutSlots - 1>();  // this slot's last stores have read it
+                    asm volatile("bar.sync 2, %0;" ::"n"(kDrainThreads) : "memory");
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float4 s4 = sb4[j];
-                        const float v0 = __fmul_rn(__fmul_rn(__int2float_rn((int)acc_r[4 * j + 0]), sa), s4.x);
-                        const float v1 = __fmul_rn(__fmul_rn(__int2float_rn((int)acc_r[4 * j + 1]), sa), s4.y);
-                        const float v2 = __fmul_rn(__fmul_rn(__int2float_rn((int)acc_r[4 * j + 2]), sa), s4.z);
-                        const float v3 = __fmul_rn(__fmul_rn(__int2float_rn((int)acc_r[4 * j + 3]), sa), s4.w);
-                        packed[2 * j] = pack_bf16x2_rn(v0, v1);
-                        packed[2 * j + 1] = pack_bf16x2_rn(v2, v3);
+                    for (int h = 0; h < 2; ++h) {
+                        const int cc = 2 * sl + h;
+                        uint32_t acc_r[32];
+                        __syncwarp();
+                        ptx::tmem_ld_32x32b_x32(t_lane + cc * 32, acc_r);
+                        ptx::tmem_ld_wait();
+                        const float4* sb4 = reinterpret_cast<const float4*>(sbs + cc * 32);
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 s4 = sb4[j];
+                            const float v0 = __fmul_rn(__fmul_rn(__int2float_rn((int)acc_r[4 * j + 0]), sa), s4.x);
+                            const float v1 = __fmul_rn(__fmul_rn(__int2float_rn((int)acc_r[4 * j + 1]), sa), s4.y);
+                            const float v2 = __fmul_rn(__fmul_rn(__int2float_rn((int)acc_r[4 * j + 2]), sa), s4.z);
+                            const float v3 = __fmul_rn(__fmul_rn(__int2float_rn((int)acc_r[4 * j + 3]), sa), s4.w);
+                            packed[2 * j] = pack_bf16x2_rn(v0, v1);
+                            packed[2 * j + 1] = pack_bf16x2_rn(v2, v3);
+                        }
+                        const uint32_t row_base = slab + (uint32_t)r * 128u;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t phys = ((uint32_t)h * 4u + j) ^ (uint32_t)(r & 7);
+                            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + phys * 16u),
+                                         "r"(packed[4 * j]), "r"(packed[4 * j + 1]), "r"(packed[4 * j + 2]),
+                                         "r"(packed[4 * j + 3])
+                                         : "memory");
+                        }
                     }
-                    const uint32_t slab = out_base + (uint32_t)(cc >> 1) * (128u * 128u) + (uint32_t)r * 128u;
-                    const uint32_t chunk0 = (uint32_t)(cc & 1) * 4u;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint32_t phys = (chunk0 + j) ^ (uint32_t)(r & 7);
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(slab + phys * 16u),
-                                     "r"(packed[4 * j]), "r"(packed[4 * j + 1]), "r"(packed[4 * j + 2]),
-                                     "r"(packed[4 * j + 3])
-                                     : "memory");
+                    ptx::fence_proxy_async_smem();  // the staged slab becomes visible to the TMA engine
+                    asm volatile("bar.sync 2, %0;" ::"n"(kDrainThreads) : "memory");
+                    if (issuer) {
+                        const int y = mt * 256 + (int)rank * 128;
+                        if (n0 + sl * 64 < p.N)
+                            for (int d = 0; d < smaps.count; ++d) ptx::tma_store_2d(&smaps.m[d], n0 + sl * 64, y, slab);
+                        ptx::bulk_commit_group();  // one group per slab, empty or not, keeps the ring count in step
                     }
-                }
-                ptx::fence_proxy_async_smem();  // the staged tile becomes visible to the TMA engine
-                asm volatile("bar.sync 2, %0;" ::"n"(kDrainThreads) : "memory");
-                if (warp == 2 && lane == 0) {
-                    const int y = mt * 256 + (int)rank * 128;
-                    for (int d = 0; d < smaps.count; ++d)
-#pragma unroll
-                        for (int sl = 0; sl < 4; ++sl)
-                            if (n0 + sl * 64 < p.N)
-                                ptx::tma_store_2d(&smaps.m[d], n0 + sl * 64, y, out_base + (uint32_t)sl * (128u * 128u));
-                    ptx::bulk_commit_group();
+                    if (++out_slot == L::kOutSlots) out_slot = 0;
                 }
             }
+            ptx::tc_fence_before_sync();  // the accumulator reads above are ordered before the release below
             if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;

@@ -102,6 +102,33 @@ int make_tile_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K,
     return 0;
 }
 
+// The status word's mirror in mapped host memory: allocated (host memory only) and published to the
+// device on the first GEMM launch on each device.  A kernel whose bounded wait gives up writes its
+// code there as well, so a later launch can refuse to go on without synchronising anything.
+volatile int* host_status_mirror() {
+    static volatile int* mirror[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (mirror[dev] != nullptr) return mirror[dev];
+    std::lock_guard<std::mutex> lock(mu);
+    if (mirror[dev] != nullptr) return mirror[dev];
+    int* host = nullptr;
+    int* device_view = nullptr;
+    if (cudaHostAlloc(reinterpret_cast<void**>(&host), sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer(reinterpret_cast<void**>(&device_view), host, 0) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    *host = 0;
+    if (cudaMemcpyToSymbol(g_host_status_mirror, &device_view, sizeof device_view) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    mirror[dev] = host;
+    return mirror[dev];
+}
+
 int sm_count() {
     static thread_local int cached_dev = -1, cached = 0;
     int dev = 0;
@@ -307,7 +334,21 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
             return fail(DSV4_ERR_ARG, "grouped_gemm: group scales need K % 128 == 0 and sa_groups == K / 128");
     }
 
+    // a kernel launched earlier on this device gave up a bounded wait: say so once instead of launching
+    if (volatile int* mirror = host_status_mirror()) {
+        const int site = *mirror;
+        if (site != 0) {
+            *mirror = 0;
+            static thread_local char msg[160];
+            snprintf(msg, sizeof msg, "w8a8_gemm: an earlier kernel on this device gave up a bounded wait (site %d); "
+                     "nothing was launched; dsv4_device_status reads and clears the device's word", site);
+            return fail(DSV4_ERR_DEVICE_WAIT, msg);
+        }
+    }
+
     Params p;
+    p.wait_limit_ns = a.test_wait_limit_ns ? a.test_wait_limit_ns : ptx::kWaitLimitNs;
+    p.withhold_loads = a.test_withhold_loads;
     p.sa = a.sa; p.sb = a.sb; p.C = a.C; p.offsets = a.offsets;
     p.M = a.M; p.N = a.N; p.K = a.K; p.E = grouped ? a.E : 1;
     p.ldc = a.ldc > 0 ? a.ldc : a.N;
@@ -450,6 +491,7 @@ int read_device_status(cudaStream_t st, int* out) {
     if (v != 0) {
         const int zero = 0;
         cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+        if (volatile int* mirror = host_status_mirror()) *mirror = 0;
     }
     if (v == 0) {
         const int rc = read_row_status(&v);

@@ -64,14 +64,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        if (ptx::elect_one()) {
+        if (!p.withhold_loads && ptx::elect_one()) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
                 const TileCoord c = sched.at(t, BN);
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u) || *abort_flag) {
+                    if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, p.wait_limit_ns) || *abort_flag) {
                         report_wait_failure(kWaitEmptyStage);
                         *abort_flag = 1;
                         ok = false;
@@ -96,7 +96,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t acc_phase = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
-                if (!ptx::mbar_wait_bounded(acc_empty_bar(acc), acc_phase ^ 1u) || *abort_flag) {
+                if (!ptx::mbar_wait_bounded(acc_empty_bar(acc), acc_phase ^ 1u, p.wait_limit_ns) || *abort_flag) {
                     report_wait_failure(kWaitAccEmpty);
                     *abort_flag = 1;
                     break;
@@ -104,7 +104,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!ptx::mbar_wait_bounded(full_bar(stage), phase) || *abort_flag) {
+                    if (!ptx::mbar_wait_bounded(full_bar(stage), phase, p.wait_limit_ns) || *abort_flag) {
                         report_wait_failure(kWaitFullStage);
                         *abort_flag = 1;
                         ok = false;
@@ -145,7 +145,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     sbs[j] = (c.n0 + j < p.N) ? __ldg(sb_row + c.n0 + j) : 0.0f;
             }
             __syncwarp();
-            bool got = ptx::mbar_wait_bounded(acc_full_bar(acc), acc_phase);
+            bool got = ptx::mbar_wait_bounded(acc_full_bar(acc), acc_phase, p.wait_limit_ns);
             if (!got || *abort_flag) {
                 report_wait_failure(kWaitAccFull);
                 *abort_flag = 1;

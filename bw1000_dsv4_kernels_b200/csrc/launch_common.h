@@ -37,6 +37,10 @@ struct GemmArgs {
     int out_i32;          // 1 = write raw int32 accumulators
     void* peerC[7];       // fused all-gather: the other ranks' mapped output slabs
     int npeers;           // 0 = none
+    // Test hook, zero through every public entry point: the tile producers of the launch issue no
+    // loads and every bounded wait gives up after test_wait_limit_ns, so the kernel's give-up path runs.
+    int test_withhold_loads = 0;
+    unsigned long long test_wait_limit_ns = 0;
 };
 int gemm_i8(const GemmArgs& a, cudaStream_t st);
 int scale_convert(const void* acc, const void* sa, const void* sb, void* out, int M, int N,

@@ -58,14 +58,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     return t;
 }
 
-// Bounded wait: gives up after about two seconds (or 2^30 polls) and returns false.
-// The caller records the failure and leaves its loop; nothing spins forever.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+// Bounded wait: gives up after limit_ns (about two seconds unless the caller passes its own limit;
+// at most 2^30 polls) and returns false.  The caller records the failure and leaves its loop;
+// nothing spins forever.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     for (uint32_t it = 1; it < (1u << 30); ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 1023u) == 0 && global_timer_ns() - t0 > 2000000000ull) return false;
+        if ((it & 63u) == 0 && global_timer_ns() - t0 > limit_ns) return false;
     }
     return false;
 }
@@ -104,6 +106,26 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, int x, int y, uin
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // all earlier groups have finished READING their shared-memory source
 __device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all but the N most recent groups have finished reading their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+// Barrier over `threads` threads (named barrier `id`) that also returns the AND of every thread's
+// predicate: how a group of warps takes one common decision (e.g. "did anybody's wait give up?").
+template <int ID, int THREADS>
+__device__ __forceinline__ bool barrier_and(bool pred) {
+    uint32_t out;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.b32 q, %1, 0;\n"
+        "barrier.cta.red.and.pred p, %2, %3, q;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(out)
+        : "r"((uint32_t)pred), "n"(ID), "n"(THREADS)
+        : "memory");
+    return out != 0;
+}
 // all earlier groups are complete
 __device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 

@@ -27,6 +27,11 @@ def column_range(rank: int, world: int, n: int):
     return rank * per, (rank + 1) * per
 
 
+def peer_order(rank: int, world: int):
+    """The other ranks in the order rank+1, rank+2, ... (mod world)."""
+    return [(rank + 1 + d) % world for d in range(world - 1)]
+
+
 class ColumnParallelW8A8Linear:
     def __init__(self, w_local, w_scale_local, rank: int = 0, world: int = 1, process_group=None):
         """w_local int8 [N/G, K], w_scale_local fp32 [N/G] (this rank's rows of the weight)."""
@@ -70,31 +75,58 @@ class ColumnParallelW8A8Linear:
 class FusedColumnParallelW8A8Linear(ColumnParallelW8A8Linear):
     """Same layer with the exchange fused into the GEMM: the output [M, N] lives in symmetric
     memory (every rank's buffer is mapped into every other rank), and the GEMM's tile epilogue
-    stages each 128 x 256 bf16 tile of this rank's column slab in shared memory and sends it with
-    TMA tile stores into all G buffers over NVLink (`w8a8_gemm_allgather`), so the transfer
-    overlaps the tensor-core work tile by tile and the result is row-major without a gather or a
-    permute.  A symmetric-memory barrier on the stream
-    before the kernel keeps a rank from overwriting rows a slower peer is still reading from the
-    previous call, and one after it makes every slab visible before anyone reads a full row."""
+    stages each bf16 tile of this rank's column slab in shared memory, 64 columns at a time, and
+    sends it with TMA tile stores into all G buffers over NVLink (`w8a8_gemm_allgather`), so the
+    transfer overlaps the tensor-core work tile by tile and the result is row-major without a
+    gather or a permute.
 
-    def __init__(self, w_local, w_scale_local, rank, world, m_max, device, process_group=None):
+    Ordering between ranks: a symmetric-memory barrier on the stream after the kernel makes every
+    slab visible before anyone reads a full row.  Nothing may overwrite rows that a slower peer is
+    still reading from an earlier call; with `buffers=2` (default) consecutive calls alternate
+    between two output buffers, and the barrier that ends call i already proves that every rank
+    has finished the work it queued before call i, i.e. its reads of call i-1's buffer, so call
+    i+1 can write that buffer without a barrier in front.  The result of a call therefore stays
+    valid until the call after the next one starts.  With `buffers=1` a second barrier before the
+    kernel gives the same protection for a single buffer.
+
+    Every rank sends its tiles to the peers in the order rank+1, rank+2, ... (mod G), so that at
+    any moment the G senders aim at G different receivers."""
+
+    def __init__(self, w_local, w_scale_local, rank, world, m_max, device, process_group=None, buffers: int = 2,
+                 rotate_peers: bool = True):
         super().__init__(w_local, w_scale_local, rank, world, process_group)
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
+        assert buffers in (1, 2)
         self.n = self.n_local * world
         self._symm = symm_mem
-        self.out = symm_mem.empty((m_max, self.n), dtype=torch.bfloat16, device=device)
         group = process_group if process_group is not None else dist.group.WORLD
-        self.handle = symm_mem.rendezvous(self.out, group=group)
-        ptrs = list(self.handle.buffer_ptrs)
-        self.peer_ptrs = [int(p) for r, p in enumerate(ptrs) if r != rank]
+        self.outs, self.handles, self.peer_ptrs = [], [], []
+        order = peer_order(rank, world) if rotate_peers else [r for r in range(world) if r != rank]
+        for _ in range(buffers):
+            out = symm_mem.empty((m_max, self.n), dtype=torch.bfloat16, device=device)
+            handle = symm_mem.rendezvous(out, group=group)
+            ptrs = list(handle.buffer_ptrs)
+            self.outs.append(out)
+            self.handles.append(handle)
+            self.peer_ptrs.append([int(ptrs[r]) for r in order])
+        self._turn = 0
+
+    @property
+    def out(self):
+        """The buffer the most recent call wrote."""
+        return self.outs[(self._turn - 1) % len(self.outs)]
 
     def forward(self, x):
         ext = _ext()
         m = x.shape[0]
-        assert m <= self.out.shape[0], "batch larger than the symmetric output buffer"
+        b = self._turn % len(self.outs)
+        out, handle = self.outs[b], self.handles[b]
+        assert m <= out.shape[0], "batch larger than the symmetric output buffer"
         q, s = ext.per_token_quant_int8(x)
-        self.handle.barrier(channel=0)
-        ext.w8a8_gemm_allgather(q, self.w, s, self.w_scale, self.out[:m], self.rank * self.n_local, self.peer_ptrs)
-        self.handle.barrier(channel=1)
-        return self.out[:m]
+        if len(self.outs) == 1:
+            handle.barrier(channel=0)
+        ext.w8a8_gemm_allgather(q, self.w, s, self.w_scale, out[:m], self.rank * self.n_local, self.peer_ptrs[b])
+        handle.barrier(channel=1)
+        self._turn += 1
+        return out[:m]

@@ -12,7 +12,7 @@ import os
 import numpy as np
 import torch
 
-from bw1000_dsv4_kernels_b200 import workloads as wl
+from tests import workloads as wl
 from oracle import cpu as oracle
 
 HERE = os.path.dirname(os.path.abspath(__file__))

@@ -5,7 +5,7 @@ absolute maximum."""
 import pytest
 import torch
 
-from bw1000_dsv4_kernels_b200 import workloads as wl
+from tests import workloads as wl
 from oracle import cpu as oracle
 
 pytestmark = pytest.mark.gpu
@@ -249,10 +249,11 @@ def test_gemm_fused_allgather_stores_to_every_buffer(cabi, ext):
         assert torch.equal(b[:, :n].cpu().view(torch.int16), ref[:m2].view(torch.int16))
 
 
-@pytest.mark.parametrize("m,n", [(2048, 2560), (1900, 2592)])
+@pytest.mark.parametrize("m,n", [(2048, 2560), (1900, 2592), (4096, 3072)])
 def test_gemm_fused_allgather_tile_store_path(cabi, ext, m, n):
     # enough tiles for the CTA-pair kernel, whose fused epilogue stages the tile in shared memory and
-    # sends it with TMA tile stores; ragged M, and N that is a multiple of 32 but not of 64
+    # sends it with TMA tile stores; ragged M, and N that is a multiple of 32 but not of 64; the last
+    # case gives every CTA pair three or four tiles, so the ring of staging slabs wraps several times
     k, width, col0 = 256, 4096, 1024
     A, B, sa, sb = _operands(m, n, k, seed=m + n)
     ref = oracle.w8a8_gemm(A, B, sa, sb)

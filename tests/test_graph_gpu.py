@@ -3,7 +3,7 @@ refill the static inputs, replay, and compare with the oracle."""
 import pytest
 import torch
 
-from bw1000_dsv4_kernels_b200 import workloads as wl
+from tests import workloads as wl
 from oracle import cpu as oracle
 
 pytestmark = pytest.mark.gpu

@@ -8,7 +8,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from bw1000_dsv4_kernels_b200 import workloads as wl
+from tests import workloads as wl
 
 pytestmark = [pytest.mark.gpu,
               pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2,
@@ -37,11 +37,19 @@ def _worker(rank, world, port, ret):
         ref = tp_linear.ColumnParallelW8A8Linear(full.w, full.w_scale).forward(full.x)
         out = tp_linear.ColumnParallelW8A8Linear(inp.w, inp.w_scale, rank, world).forward(inp.x)
         assert torch.equal(out.contiguous().view(torch.int16), ref.view(torch.int16)), "NCCL all-gather result"
-        fused = tp_linear.FusedColumnParallelW8A8Linear(inp.w, inp.w_scale, rank, world, m_max=m, device=dev)
-        for _ in range(2):
-            out2 = fused.forward(inp.x)
-            torch.cuda.synchronize()
-            assert torch.equal(out2.view(torch.int16), ref.view(torch.int16)), "fused all-gather result"
+        # fused epilogue: two alternating output buffers (no barrier in front) and one buffer (barrier on
+        # both sides); three calls in a row with changing inputs, each compared with the one-GPU layer
+        x_alt = wl.randn_bf16((m, k), device=dev, seed=9)
+        ref_alt = tp_linear.ColumnParallelW8A8Linear(full.w, full.w_scale).forward(x_alt)
+        for buffers in (2, 1):
+            fused = tp_linear.FusedColumnParallelW8A8Linear(inp.w, inp.w_scale, rank, world, m_max=m, device=dev,
+                                                            buffers=buffers)
+            for call in range(3):
+                xin, want = (inp.x, ref) if call != 1 else (x_alt, ref_alt)
+                out2 = fused.forward(xin)
+                torch.cuda.synchronize()
+                assert torch.equal(out2.view(torch.int16), want.view(torch.int16)), f"fused all-gather, {buffers} buffer(s), call {call}"
+            del fused
 
         # ---- expert-parallel MoE ----
         t, h, e, inter, topk = 256, 1024, 16, 512, 4

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from bw1000_dsv4_kernels_b200 import workloads as wl
+from tests import workloads as wl
 from oracle import cpu as oracle
 from oracle import formulas as F
 

@@ -12,7 +12,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from bw1000_dsv4_kernels_b200 import workloads as wl
+from tests import workloads as wl
 
 
 def _free_port():

@@ -4,7 +4,7 @@ and through the dsv4_native_ext operators.  int8 codes and fp32 scales must be b
 import pytest
 import torch
 
-from bw1000_dsv4_kernels_b200 import workloads as wl
+from tests import workloads as wl
 from oracle import cpu as oracle
 
 pytestmark = pytest.mark.gpu
