@@ -108,6 +108,22 @@ int launch_silu_mul_masked_quant(const void* g, const void* u, const int* mask, 
     return launch_silu_mul_quant_strided(g, N, u, N, mask, nullptr, q, s, M, N, stream);
 }
 
+int launch_silu_mul_quant_masked_layout(const void* g, int64_t ldg, const void* u, int64_t ldu, const int* masked_m,
+                                        void* q, void* s, int E, int max_m, int N, dsv4_stream_t stream) {
+    if (E < 0 || max_m < 0 || (int64_t)E * max_m > INT32_MAX)
+        return fail(DSV4_ERR_ARG, "silu_and_mul_masked_post_quant: E and max_m must be non-negative and E * max_m fit in int32");
+    const int M = E * max_m;
+    if (int rc = check_rows("silu_and_mul_masked_post_quant", M, N)) return rc;
+    if (M == 0 || N == 0) return 0;
+    DSV4_REQUIRE_PTR("silu_and_mul_masked_post_quant", g);
+    DSV4_REQUIRE_PTR("silu_and_mul_masked_post_quant", u);
+    DSV4_REQUIRE_PTR("silu_and_mul_masked_post_quant", masked_m);
+    DSV4_REQUIRE_PTR("silu_and_mul_masked_post_quant", q);
+    DSV4_REQUIRE_PTR("silu_and_mul_masked_post_quant", s);
+    if (ldg < N || ldu < N) return fail(DSV4_ERR_ARG, "silu_and_mul_masked_post_quant: row stride smaller than N");
+    return silu_mul_quant(g, u, nullptr, nullptr, q, s, M, N, ldg, ldu, cs(stream), masked_m, max_m);
+}
+
 int launch_rmsnorm(void* x, int M, int N, float eps, dsv4_stream_t stream) {
     if (int rc = check_rows("rmsnorm", M, N)) return rc;
     if (M == 0 || N == 0) return 0;
@@ -192,6 +208,19 @@ int launch_grouped_gemm(const void* A, const void* W, const void* sa, const void
     GemmArgs a{};
     a.A = A; a.B = W; a.sa = static_cast<const float*>(sa); a.sb = static_cast<const float*>(sw); a.C = C;
     a.offsets = expert_offsets; a.M = R; a.N = N; a.K = K; a.E = E; a.sa_groups = sa_groups; a.out_i32 = 0;
+    return gemm_i8(a, cs(stream));
+}
+
+int launch_grouped_gemm_masked(const void* A, const void* W, const void* sa, const void* sw, const int* masked_m,
+                               void* C, int E, int max_m, int N, int K, int sa_groups, dsv4_stream_t stream) {
+    if (masked_m == nullptr) return fail(DSV4_ERR_ARG, "grouped_gemm_masked: null pointer masked_m");
+    if (E <= 0 || max_m < 0 || (int64_t)E * max_m > INT32_MAX)
+        return fail(DSV4_ERR_ARG, "grouped_gemm_masked: E must be positive, max_m non-negative and E * max_m fit in int32");
+    if (max_m == 0) return 0;
+    GemmArgs a{};
+    a.A = A; a.B = W; a.sa = static_cast<const float*>(sa); a.sb = static_cast<const float*>(sw); a.C = C;
+    a.offsets = nullptr; a.masked_m = masked_m; a.max_m = max_m;
+    a.M = E * max_m; a.N = N; a.K = K; a.E = E; a.sa_groups = sa_groups; a.out_i32 = 0;
     return gemm_i8(a, cs(stream));
 }
 

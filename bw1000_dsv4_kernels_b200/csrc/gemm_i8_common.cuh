@@ -40,7 +40,11 @@ struct Params {
     const float* sa;
     const float* sb;
     void* C;
-    const int* offsets;  // null: dense
+    const int* offsets;  // null: dense (or the masked layout)
+    // masked layout: A and C are [E, max_m, .] and expert e owns the first masked_m[e] rows of its
+    // block; null otherwise
+    const int* masked_m;
+    int max_m;
     int M, N, K, E;
     int64_t ldc;         // row stride of C in elements (>= N)
     int sa_groups;

@@ -36,6 +36,7 @@
 #include "gemm_i8_pair_kernel.cuh"
 #include "gemm_i8_gs_kernel.cuh"
 #include "gemm_i8_stream_kernels.cuh"
+#include "gemm_i8_wt_kernel.cuh"
 
 namespace w8a8 {
 
@@ -264,6 +265,24 @@ int launch_gs_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Para
     return check_launch("grouped_gemm (group-scaled)");
 }
 
+// Grouped GEMM, weights on the MMA's M axis: one CTA per SM walks the (expert, token chunk, weight tile) items.
+template <bool GS>
+int launch_wt_variant(const CUtensorMap& tmW, const WtMaps& xmaps, const Params& p, cudaStream_t st) {
+    using L = WtSmem;
+    static_assert(L::kDynamic <= 227 * 1024, "shared memory limit");
+    static bool opted_in[64] = {};
+    if (!opt_in_shared_memory(gemm_i8_wt_kernel<GS>, L::kDynamic, opted_in))
+        return fail(DSV4_ERR_LAUNCH, "grouped_gemm: cannot raise the dynamic shared memory limit");
+    int grid = sm_count();
+    if (grid <= 0) return fail(DSV4_ERR_LAUNCH, "grouped_gemm: no CUDA device");
+    // at most this many items exist, whatever the segment lengths turn out to be
+    const int64_t bound = ((int64_t)p.M / kWtChunk + p.E) * ((p.N + 127) / 128);
+    if (bound < grid) grid = (int)bound;
+    if (grid < 1) grid = 1;
+    gemm_i8_wt_kernel<GS><<<grid, GS ? 576 : 192, L::kDynamic, st>>>(tmW, xmaps, p);
+    return check_launch("grouped_gemm");
+}
+
 // bf16 [rows, cols] view with row stride ldc elements: box = 64 columns x 128 rows, 128-byte swizzle
 int make_store_map(CUtensorMap* map, void* base, uint64_t rows, uint64_t cols, uint64_t ldc) {
     EncodeTiledFn fn = encode_tiled_fn();
@@ -318,7 +337,7 @@ int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Pa
 }  // namespace
 
 int gemm_i8(const GemmArgs& a, cudaStream_t st) {
-    const bool grouped = a.offsets != nullptr;
+    const bool grouped = a.offsets != nullptr || a.masked_m != nullptr;
     if (a.M < 0 || a.N < 0 || a.K < 0) return fail(DSV4_ERR_ARG, "w8a8_gemm: negative size");
     if (a.M == 0 || a.N == 0) return 0;
     if (a.K == 0) return fail(DSV4_ERR_ARG, "w8a8_gemm: K must be positive");
@@ -350,6 +369,7 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
     p.wait_limit_ns = a.test_wait_limit_ns ? a.test_wait_limit_ns : ptx::kWaitLimitNs;
     p.withhold_loads = a.test_withhold_loads;
     p.sa = a.sa; p.sb = a.sb; p.C = a.C; p.offsets = a.offsets;
+    p.masked_m = a.masked_m; p.max_m = a.max_m;
     p.M = a.M; p.N = a.N; p.K = a.K; p.E = grouped ? a.E : 1;
     p.ldc = a.ldc > 0 ? a.ldc : a.N;
     p.sa_groups = a.sa_groups; p.out_i32 = a.out_i32;
@@ -381,6 +401,19 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
     if (bn == 64 && (int64_t)tiles_m_bound * ((a.N + 63) / 64) < sms) bn = 32;
 
     CUtensorMap tmA, tmB;
+    if (grouped) {
+        if (a.masked_m != nullptr && (a.offsets != nullptr || a.max_m <= 0 || (int64_t)a.E * a.max_m != a.M))
+            return fail(DSV4_ERR_ARG, "grouped_gemm_masked: needs max_m > 0, M == E * max_m and no expert_offsets");
+        if (a.out_i32) return fail(DSV4_ERR_ARG, "grouped_gemm: raw accumulators exist only for the dense GEMM");
+        int rcw = make_tile_map(&tmB, a.B, b_rows, (uint64_t)a.K, 128);
+        if (rcw) return rcw;
+        WtMaps xmaps;
+        for (int i = 0; i < kWtMaps; ++i) {
+            rcw = make_tile_map(&xmaps.x[i], a.A, (uint64_t)a.M, (uint64_t)a.K, (uint32_t)(16 * (i + 1)));
+            if (rcw) return rcw;
+        }
+        return a.sa_groups != 1 ? launch_wt_variant<true>(tmB, xmaps, p, st) : launch_wt_variant<false>(tmB, xmaps, p, st);
+    }
     if (a.sa_groups != 1) {
         int rc3 = make_tile_map(&tmA, a.A, (uint64_t)a.M, (uint64_t)a.K, BM);
         if (rc3) return rc3;

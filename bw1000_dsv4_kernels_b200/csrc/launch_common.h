@@ -18,8 +18,10 @@ int ptgq(const void* x, void* q, void* s, int M, int K, int gs, cudaStream_t st)
 int add_rmsnorm_quant(void* res, const void* x, const void* w, void* q, void* s, int M, int K,
                       float eps, cudaStream_t st);
 int rmsnorm(void* x, int M, int K, float eps, cudaStream_t st);
+// masked_m / max_m: masked expert layout (rows are E blocks of max_m rows, the first masked_m[e] of block e valid)
 int silu_mul_quant(const void* g, const void* u, const int* mask, const int* valid_rows, void* q, void* s,
-                   int M, int N, int64_t ldg, int64_t ldu, cudaStream_t st);
+                   int M, int N, int64_t ldg, int64_t ldu, cudaStream_t st, const int* masked_m = nullptr,
+                   int max_m = 0);
 int silu_mul(const void* g, const void* u, void* out, int M, int N, int64_t ldg, int64_t ldu,
              cudaStream_t st);
 
@@ -31,6 +33,8 @@ struct GemmArgs {
     const float* sb;      // [N] or [E, N]; may be null only when out_i32
     void* C;              // bf16 [M, N] or int32 [M, N]
     const int* offsets;   // null for a dense GEMM, else expert_offsets[E+1]
+    const int* masked_m = nullptr;  // masked layout instead of offsets: A, C are [E, max_m, .], masked_m[E] on the device
+    int max_m = 0;
     int M, N, K, E;
     int64_t ldc;          // row stride of C in elements; 0 = N
     int sa_groups;        // 1 = per-token scale; K/128 = one scale per 128 of K

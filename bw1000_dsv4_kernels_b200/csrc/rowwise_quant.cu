@@ -438,6 +438,24 @@ __global__ void __launch_bounds__(kSumLanes) rmsnorm_generic_kernel(__nv_bfloat1
     }
 }
 
+// Which rows a masked launch touches: a per-row flag list (hip_kernels/dsv4_all_hip_kernels.hip:172-196),
+// and/or the masked expert layout, where the rows are E blocks of max_m and expert e's block holds
+// masked_m[e] valid rows at its start.  Skipped rows are neither read nor written.
+struct RowFilter {
+    const int* mask;       // null: no flag list
+    const int* masked_m;   // null: no masked layout
+    int max_m;
+    __device__ __forceinline__ bool any() const { return mask != nullptr || masked_m != nullptr; }
+    __device__ __forceinline__ bool active(int row) const {
+        if (mask != nullptr && mask[row] == 0) return false;
+        if (masked_m != nullptr) {
+            const int e = row / max_m;
+            return row - e * max_m < masked_m[e];
+        }
+        return true;
+    }
+};
+
 // ====================================================================================
 // silu_mul_quant (+ optional row mask)
 // (reference: hip_kernels/dsv4_native_ext.cpp:79-98,
@@ -452,7 +470,7 @@ __global__ void __launch_bounds__(kSumLanes) rmsnorm_generic_kernel(__nv_bfloat1
 template <int T, int MINB>
 __global__ void __launch_bounds__(T, MINB) silu_mul_quant_vec_kernel(
     const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
-    const int* __restrict__ mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
+    const RowFilter mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
     float* __restrict__ s, int M, int N, int64_t ldg, int64_t ldu) {
     ptx::grid_launch_dependents();  // a GEMM launched to overlap this kernel may start its set-up and weight loads
     extern __shared__ float4 h_row4[];  // N floats, 16-byte aligned
@@ -460,7 +478,7 @@ __global__ void __launch_bounds__(T, MINB) silu_mul_quant_vec_kernel(
     const int V = N >> 3, tid = threadIdx.x;
     if (valid_rows != nullptr) M = min(M, __ldg(valid_rows));
     for (int row = blockIdx.x; row < M; row += gridDim.x) {
-        if (mask != nullptr && mask[row] == 0) continue;  // uniform over the block
+        if (!mask.active(row)) continue;  // uniform over the block
         const uint4* gr = reinterpret_cast<const uint4*>(g + (int64_t)row * ldg);
         const uint4* ur = reinterpret_cast<const uint4*>(u + (int64_t)row * ldu);
         float am = 0.0f;
@@ -516,7 +534,7 @@ __global__ void __launch_bounds__(T, MINB) silu_mul_quant_vec_kernel(
 template <int T, int MINB>
 __global__ void __launch_bounds__(T, MINB) silu_mul_quant_table_kernel(
     const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
-    const int* __restrict__ mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
+    const RowFilter mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
     float* __restrict__ s, int M, int N, int64_t ldg, int64_t ldu) {
     ptx::grid_launch_dependents();  // a GEMM launched to overlap this kernel may start its set-up and weight loads
     extern __shared__ float4 h_row4[];
@@ -528,7 +546,7 @@ __global__ void __launch_bounds__(T, MINB) silu_mul_quant_table_kernel(
     for (int i = tid; i < kSigTabEntries; i += T) tab[i] = silu_table_entry(i);
     __syncthreads();
     for (int row = blockIdx.x; row < M; row += gridDim.x) {
-        if (mask != nullptr && mask[row] == 0) continue;  // uniform over the block
+        if (!mask.active(row)) continue;  // uniform over the block
         const uint4* gr = reinterpret_cast<const uint4*>(g + (int64_t)row * ldg);
         const uint4* ur = reinterpret_cast<const uint4*>(u + (int64_t)row * ldu);
         float am = 0.0f;
@@ -600,7 +618,7 @@ __device__ __forceinline__ void group_barrier(int id, int threads) {
 template <int RPB, int VPT>
 __global__ void __launch_bounds__(1024, 1) silu_mul_quant_async_kernel(
     const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
-    const int* __restrict__ mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
+    const RowFilter mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
     float* __restrict__ s, int M, int N, int64_t ldg, int64_t ldu) {
     ptx::grid_launch_dependents();  // a GEMM launched to overlap this kernel may start its set-up and weight loads
     constexpr int GROUP = 512, GT = GROUP / RPB, WPG = GT / 32;  // threads per group / per row, warps per row
@@ -620,10 +638,10 @@ __global__ void __launch_bounds__(1024, 1) silu_mul_quant_async_kernel(
     // 1.0f that the compiler cannot see through (N is positive): see quant_rn_lowbyte2
     const float2 one2 = splat2(__int_as_float(0x3f800000 | (N >> 31)));
 
-    auto row_active = [&](int row) { return row < M && (mask == nullptr || mask[row] != 0); };
+    auto row_active = [&](int row) { return row < M && mask.active(row); };
     // gate_up rows of a packed [M, 2N] tensor follow one another in memory exactly as in the buffer
     // ([row][gates | ups]): a block of short rows without a mask then comes in with ONE copy
-    const bool block_copy = RPB > 1 && mask == nullptr && u == g + N && ldg == ldu && ldg == 2 * (int64_t)N;
+    const bool block_copy = RPB > 1 && !mask.any() && u == g + N && ldg == ldu && ldg == 2 * (int64_t)N;
     // the group's first thread: arm the barrier with the bytes to come and start the copies.  The
     // buffer is only ever written by these copies; the kernel reads it.
     auto issue = [&](int rb) {
@@ -732,13 +750,13 @@ __global__ void __launch_bounds__(1024, 1) silu_mul_quant_async_kernel(
 
 __global__ void __launch_bounds__(256) silu_mul_quant_generic_kernel(
     const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
-    const int* __restrict__ mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
+    const RowFilter mask, const int* __restrict__ valid_rows, int8_t* __restrict__ q,
     float* __restrict__ s, int M, int N, int64_t ldg, int64_t ldu) {
     ptx::grid_launch_dependents();  // a GEMM launched to overlap this kernel may start its set-up and weight loads
     __shared__ float red[32];
     if (valid_rows != nullptr) M = min(M, __ldg(valid_rows));
     for (int row = blockIdx.x; row < M; row += gridDim.x) {
-        if (mask != nullptr && mask[row] == 0) continue;
+        if (!mask.active(row)) continue;
         const __nv_bfloat16* gr = g + (int64_t)row * ldg;
         const __nv_bfloat16* ur = u + (int64_t)row * ldu;
         float am = 0.0f;
@@ -941,9 +959,10 @@ int rmsnorm(void* x, int M, int K, float eps, cudaStream_t st) {
     return check_launch("rmsnorm");
 }
 
-int silu_mul_quant(const void* g, const void* u, const int* mask, const int* valid_rows, void* q, void* s,
-                   int M, int N, int64_t ldg, int64_t ldu, cudaStream_t st) {
+int silu_mul_quant(const void* g, const void* u, const int* row_mask, const int* valid_rows, void* q, void* s,
+                   int M, int N, int64_t ldg, int64_t ldu, cudaStream_t st, const int* masked_m, int max_m) {
     if (M == 0 || N == 0) return 0;
+    const RowFilter mask{row_mask, masked_m, max_m};
     auto gp = static_cast<const __nv_bfloat16*>(g);
     auto up = static_cast<const __nv_bfloat16*>(u);
     auto qp = static_cast<int8_t*>(q);

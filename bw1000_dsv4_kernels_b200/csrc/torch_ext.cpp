@@ -172,6 +172,32 @@ std::vector<Tensor> silu_mul_masked_quant_stream(Tensor gate, Tensor up, Tensor 
     return {q, s.unsqueeze(-1)};
 }
 
+// masked expert layout (the engine's silu_and_mul_masked_post_quant, DSV4_OPERATOR_ANALYSIS.md:45):
+// gate, up [E, max_m, N] (e.g. the halves of a packed [E, max_m, 2N] tensor), masked_m int32 [E];
+// only the first masked_m[e] rows of expert e are processed, the rest of q and s is returned as zero.
+std::vector<Tensor> silu_and_mul_masked_post_quant_stream(Tensor gate, Tensor up, Tensor masked_m, int64_t stream_ptr) {
+    check_cuda(gate, "gate", torch::kBFloat16);
+    check_cuda(up, "up", torch::kBFloat16);
+    check_cuda(masked_m, "masked_m", torch::kInt32);
+    check_same_device(gate, up, "gate/up");
+    check_same_device(gate, masked_m, "gate/masked_m");
+    TORCH_CHECK(gate.dim() == 3 && up.dim() == 3 && gate.sizes() == up.sizes(), "gate and up must be [E, max_m, N]");
+    const int64_t E = gate.size(0), max_m = gate.size(1), N = gate.size(2);
+    TORCH_CHECK(masked_m.is_contiguous() && masked_m.numel() == E, "masked_m must be a contiguous int32 tensor of E entries");
+    // rows of all experts must form one strided 2-D view: [E * max_m, N] with a single row stride
+    TORCH_CHECK(N == 0 || (gate.stride(2) == 1 && up.stride(2) == 1), "gate and up must have unit stride in the last dimension");
+    TORCH_CHECK(max_m <= 1 || E <= 1 || (gate.stride(0) == max_m * gate.stride(1) && up.stride(0) == max_m * up.stride(1)),
+                "gate and up must be views whose expert blocks follow one another (stride(0) == max_m * stride(1))");
+    c10::cuda::CUDAGuard guard(gate.device());
+    auto q = torch::zeros({E, max_m, N}, gate.options().dtype(torch::kInt8));
+    auto s = torch::zeros({E, max_m}, gate.options().dtype(torch::kFloat32));
+    check_status(launch_silu_mul_quant_masked_layout(gate.data_ptr(), gate.stride(1), up.data_ptr(), up.stride(1),
+                                                     static_cast<const int*>(masked_m.data_ptr()), q.data_ptr(),
+                                                     s.data_ptr(), to_int(E, "E"), to_int(max_m, "max_m"), to_int(N, "N"),
+                                                     as_stream(stream_ptr)));
+    return {q, s.unsqueeze(-1)};
+}
+
 // ---- add_rmsnorm_quant (reference wrapper :361-373): res is overwritten with res+x --
 std::vector<Tensor> add_rmsnorm_quant_stream(Tensor res, Tensor x, Tensor w, double eps, int64_t stream_ptr) {
     TORCH_CHECK(res.is_contiguous());
@@ -285,6 +311,53 @@ Tensor grouped_gemm_impl(Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor expert
 
 Tensor grouped_gemm_stream(Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor expert_offsets, int64_t stream_ptr) {
     return grouped_gemm_impl(A, W, sa, sw, expert_offsets, c10::nullopt, stream_ptr);
+}
+
+// masked expert layout (the engine's m_grouped_w8a8_gemm_nt_masked, DSV4_OPERATOR_ANALYSIS.md:43):
+// A int8 [E, max_m, K], W int8 [E, N, K], sa fp32 [E, max_m(, 1)] or [E, max_m, K/128], sw fp32 [E, N],
+// masked_m int32 [E] -> bf16 [E, max_m, N]; rows at or beyond masked_m[e] keep what `out` held (zero
+// when the operator allocates the output).
+Tensor grouped_gemm_masked_stream(Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor masked_m, c10::optional<Tensor> out,
+                                  int64_t stream_ptr) {
+    check_cuda(A, "A", torch::kInt8);
+    check_cuda(W, "W", torch::kInt8);
+    check_cuda(sa, "sa", torch::kFloat32);
+    check_cuda(sw, "sw", torch::kFloat32);
+    check_cuda(masked_m, "masked_m", torch::kInt32);
+    check_same_device(A, W, "A/W");
+    check_same_device(A, sa, "A/sa");
+    check_same_device(A, sw, "A/sw");
+    check_same_device(A, masked_m, "A/masked_m");
+    TORCH_CHECK(A.dim() == 3 && W.dim() == 3, "A must be [E,max_m,K] and W [E,N,K]");
+    TORCH_CHECK(A.is_contiguous() && W.is_contiguous() && sa.is_contiguous() && sw.is_contiguous() && masked_m.is_contiguous(),
+                "A, W, sa, sw and masked_m must be contiguous");
+    const int E = to_int(A.size(0), "E"), max_m = to_int(A.size(1), "max_m"), K = to_int(A.size(2), "K");
+    const int N = to_int(W.size(1), "N");
+    TORCH_CHECK(W.size(0) == E && W.size(2) == K, "A and W disagree on E or K");
+    TORCH_CHECK(sw.numel() == (int64_t)E * N, "sw must be [E,N]");
+    TORCH_CHECK(masked_m.numel() == E, "masked_m must have E entries");
+    int groups = 1;
+    if (sa.numel() != (int64_t)E * max_m) {
+        TORCH_CHECK(K % 128 == 0 && sa.numel() == (int64_t)E * max_m * (K / 128),
+                    "sa must have E*max_m entries (per token) or be [E, max_m, K/128] (per 128-wide group)");
+        groups = K / 128;
+    }
+    c10::cuda::CUDAGuard guard(A.device());
+    Tensor C;
+    if (out.has_value()) {
+        C = *out;
+        check_cuda(C, "out", torch::kBFloat16);
+        check_same_device(A, C, "A/out");
+        TORCH_CHECK(C.is_contiguous() && C.dim() == 3 && C.size(0) == E && C.size(1) == max_m && C.size(2) == N,
+                    "out must be a contiguous bf16 [E, max_m, N] tensor");
+    } else {
+        C = torch::zeros({E, max_m, N}, A.options().dtype(torch::kBFloat16));
+    }
+    if (E == 0 || max_m == 0 || N == 0) return C;
+    check_status(launch_grouped_gemm_masked(A.data_ptr(), W.data_ptr(), sa.data_ptr(), sw.data_ptr(),
+                                            static_cast<const int*>(masked_m.data_ptr()), C.data_ptr(), E, max_m, N, K,
+                                            groups, as_stream(stream_ptr)));
+    return C;
 }
 
 std::vector<Tensor> moe_segments_impl(Tensor topk_ids, int64_t num_experts, int64_t expert_lo,
@@ -502,6 +575,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         return grouped_gemm_stream(A, W, sa, sw, off, current_stream_ptr());
     });
     m.def("grouped_gemm_stream", &grouped_gemm_stream);
+    m.def("grouped_gemm_masked", [](Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor masked_m, c10::optional<Tensor> out) {
+        return grouped_gemm_masked_stream(A, W, sa, sw, masked_m, out, current_stream_ptr());
+    }, py::arg("A"), py::arg("W"), py::arg("sa"), py::arg("sw"), py::arg("masked_m"), py::arg("out") = py::none());
+    m.def("grouped_gemm_masked_stream", &grouped_gemm_masked_stream);
+    // the engine's names for the two masked-layout operators
+    m.def("m_grouped_w8a8_gemm_nt_masked", [](Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor masked_m, c10::optional<Tensor> out) {
+        return grouped_gemm_masked_stream(A, W, sa, sw, masked_m, out, current_stream_ptr());
+    }, py::arg("A"), py::arg("W"), py::arg("sa"), py::arg("sw"), py::arg("masked_m"), py::arg("out") = py::none());
+    m.def("silu_and_mul_masked_post_quant", [](Tensor g, Tensor u, Tensor masked_m) {
+        return silu_and_mul_masked_post_quant_stream(g, u, masked_m, current_stream_ptr());
+    });
+    m.def("silu_and_mul_masked_post_quant_stream", &silu_and_mul_masked_post_quant_stream);
     m.def("grouped_gemm_into", [](Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor off, Tensor out) {
         return grouped_gemm_impl(A, W, sa, sw, off, out, current_stream_ptr());
     });

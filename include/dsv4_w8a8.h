@@ -101,6 +101,16 @@ DSV4_API int launch_silu_mul_quant_strided(const void* g, int64_t ldg, const voi
                                   const int* mask, const int* valid_rows, void* q, void* s, int M,
                                   int N, dsv4_stream_t stream);
 
+/* The same on the masked expert layout of an expert-parallel prefill: the rows are E blocks of max_m
+ * (g, u: [E * max_m, N] with row strides ldg, ldu, e.g. the halves of one packed [E, max_m, 2N] tensor),
+ * masked_m int32 [E] ON THE DEVICE, and only the first masked_m[e] rows of block e are processed
+ * (q int8 [E * max_m, N] and s fp32 [E * max_m] of the other rows are untouched; values above max_m
+ * count as max_m).  The engine's silu_and_mul_masked_post_quant (DSV4_OPERATOR_ANALYSIS.md:45), whose
+ * kernel in the reference takes a per-row flag list instead (dsv4_all_hip_kernels.hip:172-196). */
+DSV4_API int launch_silu_mul_quant_masked_layout(const void* g, int64_t ldg, const void* u, int64_t ldu,
+                                        const int* masked_m, void* q, void* s, int E, int max_m, int N,
+                                        dsv4_stream_t stream);
+
 /* ---- unfused neighbours --------------------------------------------------------- */
 
 /* x <- x * rsqrt(mean(x^2) + eps), in place, no gamma.
@@ -157,7 +167,8 @@ DSV4_API int launch_scale_convert(const void* int_out, const void* sa, const voi
 /* ---- MoE grouped GEMM ----------------------------------------------------------- */
 
 /* Rows of A are sorted by expert; expert e owns rows [expert_offsets[e], expert_offsets[e+1])
- * (int32, on the device, E+1 entries, non-decreasing, last = R).
+ * (int32, on the device, E+1 entries, non-decreasing, last <= R; rows past R and experts whose
+ * entries decrease are skipped rather than trusted).
  *   sa_groups == 1 : C[r,n] = bf16((float(acc[r,n]) * sa[r]) * sw[e,n])
  *   sa_groups == K/128 : sa is [R, K/128];
  *       C[r,n] = bf16(y * sw[e,n]),  y = fma(float(acc_g[r,n]), sa[r,g], y) for g = 0,1,...
@@ -168,6 +179,16 @@ DSV4_API int launch_scale_convert(const void* int_out, const void* sa, const voi
 DSV4_API int launch_grouped_gemm(const void* A, const void* W, const void* sa, const void* sw,
                         const int* expert_offsets, void* C, int R, int E, int N, int K,
                         int sa_groups, dsv4_stream_t stream);
+
+/* The same product on the masked expert layout that the engine's prefill GEMM
+ * m_grouped_w8a8_gemm_nt_masked takes (DSV4_OPERATOR_ANALYSIS.md:43; the reference has no source for
+ * it): A int8 [E, max_m, K], W int8 [E, N, K], sw fp32 [E, N], C bf16 [E, max_m, N], masked_m int32 [E]
+ * ON THE DEVICE; expert e multiplies the first masked_m[e] rows of its block (values above max_m count
+ * as max_m) and leaves the other rows of C untouched.  sa fp32 [E * max_m] (sa_groups == 1) or
+ * [E * max_m, K/128] (sa_groups == K/128), arithmetic as above. */
+DSV4_API int launch_grouped_gemm_masked(const void* A, const void* W, const void* sa, const void* sw,
+                               const int* masked_m, void* C, int E, int max_m, int N, int K, int sa_groups,
+                               dsv4_stream_t stream);
 
 /* Router top-k.  logits fp32 [T,E] (E <= 1024) -> topk_ids int32 [T,k] in descending order of logit
  * (ties: lower expert index first), topk_w fp32 [T,k] = softmax over the k selected logits.

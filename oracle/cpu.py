@@ -153,6 +153,42 @@ def grouped_gemm(A, W, sa, sw, expert_offsets):
     return out
 
 
+def masked_row_flags(masked_m: torch.Tensor, max_m: int):
+    """Per-row flags [E * max_m] of the masked expert layout: row i of block e is valid iff i < masked_m[e]."""
+    m = masked_m.to(torch.int64).clamp(0, max_m).view(-1, 1)
+    return (torch.arange(max_m).view(1, -1) < m).to(torch.int32).reshape(-1)
+
+
+def silu_and_mul_masked_post_quant(gate: torch.Tensor, up: torch.Tensor, masked_m: torch.Tensor):
+    """Masked expert layout (the engine op of DSV4_OPERATOR_ANALYSIS.md:45): gate, up [E, max_m, N],
+    masked_m [E].  The reference kernel takes per-row flags (dsv4_all_hip_kernels.hip:172-196); the flags
+    here are i < masked_m[e].  -> (q [E, max_m, N], s [E, max_m, 1]), zero in the skipped rows."""
+    e, max_m, n = gate.shape
+    flags = masked_row_flags(masked_m, max_m)
+    q, s = silu_mul_quant(gate.reshape(e * max_m, n), up.reshape(e * max_m, n), flags)
+    return q.view(e, max_m, n), s.view(e, max_m, 1)
+
+
+def grouped_gemm_masked(A, W, sa, sw, masked_m, out=None):
+    """Masked expert layout (the engine op of DSV4_OPERATOR_ANALYSIS.md:43; no source in the reference):
+    A int8 [E, max_m, K], W int8 [E, N, K], sa [E, max_m] or [E, max_m, K/128], sw [E, N], masked_m [E].
+    Expert e multiplies its first masked_m[e] rows (arithmetic of grouped_gemm); other rows of `out`
+    (zero if not given) are left as they are."""
+    e, max_m, k = A.shape
+    n = W.shape[1]
+    if out is None:
+        out = torch.zeros((e, max_m, n), dtype=torch.bfloat16)
+    sa = sa.contiguous().float().view(e, max_m, -1)
+    for i in range(e):
+        m = int(min(max(int(masked_m[i]), 0), max_m))
+        if m == 0:
+            continue
+        s_i = sa[i, :m]
+        s_i = s_i.reshape(-1) if s_i.shape[-1] == 1 else s_i
+        out[i, :m] = grouped_gemm(A[i, :m], W[i:i + 1], s_i, sw[i:i + 1], torch.tensor([0, m], dtype=torch.int32))
+    return out
+
+
 def moe_segments(topk_ids: torch.Tensor, num_experts: int, expert_lo: int = 0):
     """-> (offsets [E+1], src_row [T*topk] (valid below offsets[-1]), dst_slot [T*topk] with -1 for
     pairs routed outside [expert_lo, expert_lo + num_experts))."""
