@@ -22,7 +22,7 @@ EXT_PATH = os.path.join(HERE, "dsv4_native_ext" + sysconfig.get_config_var("EXT_
 
 CUDA_SOURCES = ["rowwise_quant.cu", "gemm_i8_sm100.cu", "moe_segments.cu", "c_abi.cu"]
 CUDA_HEADERS = ["w8a8_arith.cuh", "sm100_ptx.cuh", "launch_common.h", "gemm_i8_common.cuh", "gemm_i8_tile_kernel.cuh",
-                "gemm_i8_pair_kernel.cuh", "gemm_i8_gs_kernel.cuh", "gemm_i8_stream_kernels.cuh"]
+                "gemm_i8_pair_kernel.cuh", "gemm_i8_wt_kernel.cuh", "gemm_i8_stream_kernels.cuh"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -66,11 +66,9 @@ struct Smem {
     static constexpr int kBBytes = BN * BK;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTilesBytes = STAGES * kStageBytes;
-    // after the tiles: one copy of the tile's column scales per drain warp, tile prefix,
-    // barriers, tmem slot
+    // after the tiles: one copy of the tile's column scales per drain warp, barriers, tmem slot
     static constexpr int kSbOff = kTilesBytes;
-    static constexpr int kPrefixOff = kSbOff + 4 * BN * 4;
-    static constexpr int kBarOff = kPrefixOff + (kMaxExperts + 1) * 4 + 4;  // 8-byte aligned below
+    static constexpr int kBarOff = kSbOff + 4 * BN * 4;  // 8-byte aligned below
     static constexpr int kNumBars = 2 * STAGES + 8;  // stage full/empty + up to 4 accumulator full/empty pairs
     static constexpr int kTmemSlotOff = ((kBarOff + 7) & ~7) + kNumBars * 8;
     static constexpr int kAbortOff = kTmemSlotOff + 4;
@@ -78,80 +76,35 @@ struct Smem {
     static constexpr int kDynamic = kTotal + 1024;  // slack to align the base to 1024
 };
 
-// Maps a linear tile index to (first A row, rows valid, first B row, first C column).
+// Maps a linear tile index of a dense problem to its coordinates (M fastest).
 struct TileCoord {
     int a_row0;    // first row of A / C
-    int row_end;   // one past the last valid row of this tile's segment
-    int b_row0;    // first row of B (expert * N + n0 for the grouped form)
+    int row_end;   // one past the last valid row
+    int b_row0;    // first row of B
     int n0;        // first output column
-    int expert;
 };
 
 struct Scheduler {
     const Params& p;
-    const int* prefix;  // shared: prefix[e] = m-tiles of experts < e  (grouped only)
     int tiles_n;
     int total;
 
-    __device__ Scheduler(const Params& p_, const int* prefix_, int bn) : p(p_), prefix(prefix_) {
+    __device__ Scheduler(const Params& p_, int bn) : p(p_) {
         tiles_n = (p.N + bn - 1) / bn;
-        if (p.offsets == nullptr) {
-            total = ((p.M + BM - 1) / BM) * tiles_n;
-        } else {
-            total = prefix[p.E] * tiles_n;
-        }
+        total = ((p.M + BM - 1) / BM) * tiles_n;
     }
 
     __device__ TileCoord at(int t, int bn) const {
         TileCoord c;
-        if (p.offsets == nullptr) {
-            const int tiles_m = (p.M + BM - 1) / BM;
-            const int mt = t % tiles_m, nt = t / tiles_m;
-            c.a_row0 = mt * BM;
-            c.row_end = p.M;
-            c.n0 = nt * bn;
-            c.b_row0 = c.n0;
-            c.expert = 0;
-        } else {
-            // largest e with prefix[e] * tiles_n <= t
-            int lo = 0, hi = p.E;  // invariant: prefix[lo]*tiles_n <= t < prefix[hi]*tiles_n
-            while (hi - lo > 1) {
-                const int mid = (lo + hi) >> 1;
-                if (prefix[mid] * tiles_n <= t) lo = mid; else hi = mid;
-            }
-            const int e = lo;
-            const int cnt = prefix[e + 1] - prefix[e];
-            const int local = t - prefix[e] * tiles_n;
-            const int nt = local / cnt, mt = local % cnt;
-            c.a_row0 = p.offsets[e] + mt * BM;
-            c.row_end = min(p.offsets[e + 1], p.M);  // never past the end of C, whatever the list says
-            c.n0 = nt * bn;
-            c.b_row0 = e * p.N + c.n0;
-            c.expert = e;
-        }
+        const int tiles_m = (p.M + BM - 1) / BM;
+        const int mt = t % tiles_m, nt = t / tiles_m;
+        c.a_row0 = mt * BM;
+        c.row_end = p.M;
+        c.n0 = nt * bn;
+        c.b_row0 = c.n0;
         return c;
     }
 };
-
-// One warp: prefix[e] = number of 128-row tiles of the experts before e, prefix[E] = all of them
-// (exclusive scan of ceil(segment length / 128) over the experts, into shared memory).
-__device__ __forceinline__ void build_tile_prefix(const Params& p, int* prefix, int lane) {
-    int carry = 0;
-    for (int e0 = 0; e0 < p.E; e0 += 32) {
-        const int e = e0 + lane;
-        int cnt = 0;
-        if (e < p.E) cnt = max(0, (min(p.offsets[e + 1], p.M) - p.offsets[e] + BM - 1) / BM);  // a bad list gives no tiles
-        int incl = cnt;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int v = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += v;
-        }
-        if (e < p.E) prefix[e] = carry + incl - cnt;
-        carry += __shfl_sync(0xffffffffu, incl, 31);
-    }
-    if (lane == 0) prefix[p.E] = carry;
-}
 
 __device__ __forceinline__ void report_wait_failure(int site) {
     if (atomicCAS(&g_device_status, 0, site) == 0) {

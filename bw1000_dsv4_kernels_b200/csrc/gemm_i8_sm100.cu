@@ -8,11 +8,11 @@
 //     per stage, accumulating in tensor memory; warps 2-5 drain the finished accumulator
 //     with tcgen05.ld, apply the two scales and store bf16.  Tensor memory holds two
 //     accumulators so that the drain of tile i overlaps the MMAs of tile i+1.
-//   * The grouped (MoE) form walks expert segments: the tile list is derived inside the
-//     kernel from expert_offsets (device memory), so no host synchronisation and no
-//     scratch buffer is needed.  Rows of a tile that fall past the end of a segment are
-//     computed and discarded.
-//   * The group-scaled form (one activation scale per 128 of K) cannot defer scaling to
+//   * The grouped (MoE) form puts an expert's weight rows on the MMA's M axis and its tokens
+//     on the N axis (gemm_i8_wt_kernel.cuh); its work list is derived inside the kernel from
+//     expert_offsets or masked_m (device memory), so no host synchronisation and no scratch
+//     buffer is needed.
+//   * Its group-scaled form (one activation scale per 128 of K) cannot defer scaling to
 //     the end: each 128-wide K block is one accumulator that the drain warps fold into
 //     fp32 registers as y = fma(float(acc), sa[row, g], y).
 //   * Every wait on an mbarrier is bounded; a wait that gives up records a code in a
@@ -34,18 +34,18 @@
 #include "gemm_i8_common.cuh"
 #include "gemm_i8_tile_kernel.cuh"
 #include "gemm_i8_pair_kernel.cuh"
-#include "gemm_i8_gs_kernel.cuh"
 #include "gemm_i8_stream_kernels.cuh"
 #include "gemm_i8_wt_kernel.cuh"
 
 namespace w8a8 {
 
-// Process-wide option: launch the dense GEMMs (weight-streaming kernels for M <= 256, CTA-pair kernel
-// above) so that they may overlap the kernel before them on the stream (programmatic dependent
-// launch).  Off by default.
-static std::atomic<int> g_overlap_previous{0};
-void set_overlap_previous_kernel(int on) { g_overlap_previous.store(on ? 1 : 0, std::memory_order_relaxed); }
-int overlap_previous_kernel() { return g_overlap_previous.load(std::memory_order_relaxed); }
+// Option of the calling thread: launch the dense GEMMs (weight-streaming kernels for M <= 256, CTA-pair
+// kernel above) so that they may overlap the kernel before them on the stream (programmatic dependent
+// launch).  Off by default.  Per thread, so that one thread that captures a CUDA graph with the option
+// on does not change what other threads launch meanwhile.
+static thread_local int g_overlap_previous = 0;
+void set_overlap_previous_kernel(int on) { g_overlap_previous = on ? 1 : 0; }
+int overlap_previous_kernel() { return g_overlap_previous; }
 
 namespace {
 
@@ -250,21 +250,6 @@ int launch_stream_pair(const CUtensorMap& tmW, const CUtensorMap& tmX, const Par
     return check_launch("w8a8_gemm (weight streaming, CTA pairs)");
 }
 
-template <int STAGES>
-int launch_gs_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, int max_tiles, cudaStream_t st) {
-    using L = Smem<GSN, STAGES>;
-    static_assert(L::kDynamic <= 227 * 1024, "shared memory limit");
-    static bool opted_in[64] = {};
-    if (!opt_in_shared_memory(gemm_i8_gs_kernel<STAGES>, L::kDynamic, opted_in))
-        return fail(DSV4_ERR_LAUNCH, "grouped_gemm: cannot raise the dynamic shared memory limit");
-    int grid = sm_count();
-    if (grid <= 0) return fail(DSV4_ERR_LAUNCH, "grouped_gemm: no CUDA device");
-    if (max_tiles < grid) grid = max_tiles;
-    if (grid < 1) grid = 1;
-    gemm_i8_gs_kernel<STAGES><<<grid, kGsThreads, L::kDynamic, st>>>(tmA, tmB, p);
-    return check_launch("grouped_gemm (group-scaled)");
-}
-
 // Grouped GEMM, weights on the MMA's M axis: one CTA per SM walks the (expert, token chunk, weight tile) items.
 template <bool GS>
 int launch_wt_variant(const CUtensorMap& tmW, const WtMaps& xmaps, const Params& p, cudaStream_t st) {
@@ -348,6 +333,7 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
         return fail(DSV4_ERR_ARG, "w8a8_gemm: A and B must be 16-byte aligned");
     if (grouped && (a.E <= 0 || a.E > kMaxExperts)) return fail(DSV4_ERR_ARG, "grouped_gemm: E must be in 1..1024");
     if (a.sa_groups != 1) {
+        if (!grouped) return fail(DSV4_ERR_ARG, "w8a8_gemm: group scales exist only for the grouped GEMM");
         if (a.out_i32) return fail(DSV4_ERR_ARG, "w8a8_gemm: raw accumulators exist only for per-token scaling");
         if (a.K % 128 != 0 || a.sa_groups != a.K / 128)
             return fail(DSV4_ERR_ARG, "grouped_gemm: group scales need K % 128 == 0 and sa_groups == K / 128");
@@ -391,7 +377,7 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
 
     const uint64_t b_rows = grouped ? (uint64_t)a.E * a.N : (uint64_t)a.N;
     const int sms = sm_count();
-    const int tiles_m_bound = grouped ? (a.M / BM + a.E) : (a.M + BM - 1) / BM;
+    const int tiles_m_bound = (a.M + BM - 1) / BM;
 
     // Tile width: 256 columns when that already gives every SM a tile, otherwise narrower
     // tiles so that a short, weight-streaming problem spreads over more SMs.
@@ -414,15 +400,8 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
         }
         return a.sa_groups != 1 ? launch_wt_variant<true>(tmB, xmaps, p, st) : launch_wt_variant<false>(tmB, xmaps, p, st);
     }
-    if (a.sa_groups != 1) {
-        int rc3 = make_tile_map(&tmA, a.A, (uint64_t)a.M, (uint64_t)a.K, BM);
-        if (rc3) return rc3;
-        rc3 = make_tile_map(&tmB, a.B, b_rows, (uint64_t)a.K, GSN);
-        if (rc3) return rc3;
-        return launch_gs_variant<4>(tmA, tmB, p, tiles_m_bound * ((a.N + GSN - 1) / GSN), st);
-    }
     // Few tokens: stream the weight once, tokens on the MMA's N axis, K split over a cluster
-    if (!grouped && a.M <= 256 && a.npeers == 0) {
+    if (a.M <= 256 && a.npeers == 0) {
         const int k_blocks = (a.K + BK - 1) / BK;
         if (a.M > 128 && a.N >= 256) {
             // 129..256 tokens: CTA pairs halve the token traffic per SM
@@ -456,7 +435,7 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
         }
     }
     // Dense problems with more than one 128-row tile go to the CTA-pair kernel
-    if (!grouped && a.M > 128 && (int64_t)((a.M + 255) / 256) * ((a.N + 255) / 256) >= sms / 4) {
+    if (a.M > 128 && (int64_t)((a.M + 255) / 256) * ((a.N + 255) / 256) >= sms / 4) {
         int rc2 = make_tile_map(&tmA, a.A, (uint64_t)a.M, (uint64_t)a.K, BM);
         if (rc2) return rc2;
         rc2 = make_tile_map(&tmB, a.B, b_rows, (uint64_t)a.K, 128);

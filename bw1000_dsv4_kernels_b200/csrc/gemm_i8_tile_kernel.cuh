@@ -1,5 +1,5 @@
 // Private part of gemm_i8_sm100.cu (included by that translation unit only, hence the unnamed
-// namespace): the one-CTA-per-tile kernel (dense with few tiles, grouped per-token-scaled, raw int32).
+// namespace): the one-CTA-per-tile kernel (dense problems with few tiles, raw int32 output).
 #ifndef W8A8_GEMM_I8_TILE_KERNEL_CUH
 #define W8A8_GEMM_I8_TILE_KERNEL_CUH
 
@@ -19,7 +19,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     float* sb_tile = reinterpret_cast<float*>(smem + L::kSbOff);
-    int* prefix = reinterpret_cast<int*>(smem + L::kPrefixOff);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ((L::kBarOff + 7) & ~7));
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlotOff);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
@@ -53,13 +52,12 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
         ptx::tmem_relinquish();
     }
-    if (p.offsets != nullptr && warp == 2) build_tile_prefix(p, prefix, lane);
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    const Scheduler sched(p, prefix, BN);
+    const Scheduler sched(p, BN);
     const int k_blocks = (p.K + BK - 1) / BK;
 
     if (warp == 0) {
@@ -140,9 +138,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // column scales of this tile -> this warp's shared copy
             __syncwarp();
             if (!p.out_i32) {
-                const float* sb_row = p.sb + (int64_t)c.expert * p.N;
                 for (int j = lane; j < BN; j += 32)
-                    sbs[j] = (c.n0 + j < p.N) ? __ldg(sb_row + c.n0 + j) : 0.0f;
+                    sbs[j] = (c.n0 + j < p.N) ? __ldg(p.sb + c.n0 + j) : 0.0f;
             }
             __syncwarp();
             bool got = ptx::mbar_wait_bounded(acc_full_bar(acc), acc_phase, p.wait_limit_ns);
@@ -154,7 +151,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             ptx::tc_fence_after_sync();
             const int row = c.a_row0 + quarter * 32 + lane;
             const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-            // a warp whose 32 rows all lie past the end of the segment has nothing to load or store
+            // a warp whose 32 rows all lie past the last row has nothing to load or store
             if (c.a_row0 + quarter * 32 < c.row_end)
                 drain_accumulator<BN>(p, t_lane, sbs, row, row < c.row_end, c.n0, vec_ok);
             ptx::tc_fence_before_sync();

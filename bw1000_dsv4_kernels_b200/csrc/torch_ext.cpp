@@ -7,6 +7,11 @@
 // arguments, allocates the outputs with torch and forwards plain pointers to the C-ABI
 // (include/dsv4_w8a8.h); there is no CPU path: a non-CUDA tensor raises.
 //
+// Streams: `name(...)` launches on torch's current stream; `name_stream(..., stream_ptr)` launches on the
+// given stream and copies nothing, but its outputs still come from torch's caching allocator, which ties
+// them to the CURRENT stream: a caller that passes another stream keeps the outputs alive (or calls
+// record_stream on them) until that stream has run the kernel, as with any tensor used across streams.
+//
 // Differences from the reference, all additive or stricter:
 //   * `name(...)` launches on torch's current stream rather than on stream 0;
 //   * dtype / device / shape / alignment are checked (the reference checks contiguity only);
@@ -147,6 +152,7 @@ std::vector<Tensor> silu_mul_quant_stream(Tensor gate, Tensor up, int64_t stream
 std::vector<Tensor> silu_mul_quant_rows_stream(Tensor gate, Tensor up, Tensor valid_rows, int64_t stream_ptr) {
     const GateUp g = check_gate_up(gate, up);
     check_cuda(valid_rows, "valid_rows", torch::kInt32);
+    check_same_device(gate, valid_rows, "gate/valid_rows");
     TORCH_CHECK(valid_rows.numel() >= 1, "valid_rows must hold one int32");
     c10::cuda::CUDAGuard guard(gate.device());
     auto q = torch::empty({g.M, g.N}, gate.options().dtype(torch::kInt8));
@@ -162,6 +168,7 @@ std::vector<Tensor> silu_mul_quant_rows_stream(Tensor gate, Tensor up, Tensor va
 std::vector<Tensor> silu_mul_masked_quant_stream(Tensor gate, Tensor up, Tensor mask, int64_t stream_ptr) {
     const GateUp g = check_gate_up(gate, up);
     check_cuda(mask, "mask", torch::kInt32);
+    check_same_device(gate, mask, "gate/mask");
     TORCH_CHECK(mask.is_contiguous() && mask.numel() == g.M, "mask must be a contiguous int32 tensor of M entries");
     c10::cuda::CUDAGuard guard(gate.device());
     auto q = torch::zeros({g.M, g.N}, gate.options().dtype(torch::kInt8));
@@ -232,16 +239,21 @@ GemmShape check_gemm_operands(const Tensor& A, const Tensor& B) {
     TORCH_CHECK(A.size(1) == B.size(1), "A and B disagree on K: ", A.size(1), " vs ", B.size(1));
     return {to_int(A.size(0), "M"), to_int(B.size(0), "N"), to_int(A.size(1), "K")};
 }
-Tensor flat_scale(const Tensor& s, int64_t n, const char* name) {
+// A scale vector as the launchers take it: fp32, n entries, dense, on the operands' device.  Nothing is
+// copied here: a hidden copy would run on torch's current stream, which need not be the stream the
+// `_stream` variants launch on.
+const Tensor& flat_scale(const Tensor& s, int64_t n, const char* name, const Tensor& operand) {
     check_cuda(s, name, torch::kFloat32);
+    check_same_device(s, operand, name);
     TORCH_CHECK(s.numel() == n, name, " must have ", n, " entries, got ", s.numel());
-    return s.contiguous();
+    TORCH_CHECK(s.is_contiguous(), name, " must be contiguous");
+    return s;
 }
 
 Tensor w8a8_scaled_gemm_stream(Tensor A, Tensor B, Tensor sa, Tensor sb, int64_t stream_ptr) {
     const GemmShape g = check_gemm_operands(A, B);
-    auto sa_c = flat_scale(sa, g.M, "sa");
-    auto sb_c = flat_scale(sb, g.N, "sb");
+    const Tensor& sa_c = flat_scale(sa, g.M, "sa", A);
+    const Tensor& sb_c = flat_scale(sb, g.N, "sb", A);
     c10::cuda::CUDAGuard guard(A.device());
     auto C = torch::empty({g.M, g.N}, A.options().dtype(torch::kBFloat16));
     check_status(launch_w8a8_gemm(A.data_ptr(), B.data_ptr(), sa_c.data_ptr(), sb_c.data_ptr(), C.data_ptr(), g.M,
@@ -260,8 +272,8 @@ Tensor w8a8_gemm_i32_stream(Tensor A, Tensor B, int64_t stream_ptr) {
 Tensor scale_convert_stream(Tensor acc, Tensor sa, Tensor sb, int64_t stream_ptr) {
     check_cuda(acc, "acc", torch::kInt32);
     TORCH_CHECK(acc.dim() == 2 && acc.is_contiguous(), "acc must be a contiguous [M,N] tensor");
-    auto sa_c = flat_scale(sa, acc.size(0), "sa");
-    auto sb_c = flat_scale(sb, acc.size(1), "sb");
+    const Tensor& sa_c = flat_scale(sa, acc.size(0), "sa", acc);
+    const Tensor& sb_c = flat_scale(sb, acc.size(1), "sb", acc);
     c10::cuda::CUDAGuard guard(acc.device());
     auto out = torch::empty_like(acc, acc.options().dtype(torch::kBFloat16));
     check_status(launch_scale_convert(acc.data_ptr(), sa_c.data_ptr(), sb_c.data_ptr(), out.data_ptr(),
@@ -278,6 +290,9 @@ Tensor grouped_gemm_impl(Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor expert
     check_cuda(sw, "sw", torch::kFloat32);
     check_cuda(expert_offsets, "expert_offsets", torch::kInt32);
     check_same_device(A, W, "A/W");
+    check_same_device(A, sa, "A/sa");
+    check_same_device(A, sw, "A/sw");
+    check_same_device(A, expert_offsets, "A/expert_offsets");
     TORCH_CHECK(A.dim() == 2 && W.dim() == 3, "A must be [R,K] and W [E,N,K]");
     TORCH_CHECK(A.is_contiguous() && W.is_contiguous() && sw.is_contiguous() && expert_offsets.is_contiguous(),
                 "A, W, sw and expert_offsets must be contiguous");
@@ -286,7 +301,8 @@ Tensor grouped_gemm_impl(Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor expert
     TORCH_CHECK(W.size(2) == K, "A and W disagree on K");
     TORCH_CHECK(sw.numel() == (int64_t)E * N, "sw must be [E,N]");
     TORCH_CHECK(expert_offsets.numel() == E + 1, "expert_offsets must have E+1 entries");
-    auto sa_c = sa.contiguous();
+    TORCH_CHECK(sa.is_contiguous(), "sa must be contiguous");
+    const Tensor& sa_c = sa;
     int groups = 1;
     if (sa_c.numel() != R) {
         TORCH_CHECK(K % 128 == 0 && sa_c.numel() == (int64_t)R * (K / 128),
@@ -493,8 +509,8 @@ void moe_combine_exchange_stream(std::vector<int64_t> z_ptrs, std::vector<int64_
 // w8a8 GEMM written into columns [col0, col0 + N) of an existing bf16 [M, ldc] buffer
 void w8a8_gemm_into_stream(Tensor A, Tensor B, Tensor sa, Tensor sb, Tensor out, int64_t col0, int64_t stream_ptr) {
     const GemmShape g = check_gemm_operands(A, B);
-    auto sa_c = flat_scale(sa, g.M, "sa");
-    auto sb_c = flat_scale(sb, g.N, "sb");
+    const Tensor& sa_c = flat_scale(sa, g.M, "sa", A);
+    const Tensor& sb_c = flat_scale(sb, g.N, "sb", A);
     check_cuda(out, "out", torch::kBFloat16);
     TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1 && out.size(0) == g.M && col0 >= 0 && col0 + g.N <= out.size(1),
                 "out must be a [M, >= col0 + N] bf16 tensor with unit inner stride");
@@ -510,8 +526,8 @@ void w8a8_gemm_into_stream(Tensor A, Tensor B, Tensor sa, Tensor sb, Tensor out,
 void w8a8_gemm_allgather_stream(Tensor A, Tensor B, Tensor sa, Tensor sb, Tensor out, int64_t col0,
                                 std::vector<int64_t> peer_ptrs, int64_t stream_ptr) {
     const GemmShape g = check_gemm_operands(A, B);
-    auto sa_c = flat_scale(sa, g.M, "sa");
-    auto sb_c = flat_scale(sb, g.N, "sb");
+    const Tensor& sa_c = flat_scale(sa, g.M, "sa", A);
+    const Tensor& sb_c = flat_scale(sb, g.N, "sb", A);
     check_cuda(out, "out", torch::kBFloat16);
     TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1 && out.size(0) == g.M && col0 >= 0 && col0 + g.N <= out.size(1),
                 "out must be a [M, >= col0 + N] bf16 tensor with unit inner stride");

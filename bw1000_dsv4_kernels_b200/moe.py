@@ -95,9 +95,11 @@ class W8A8MoE:
         if single:
             return self.local_partial(x, topk_ids, topk_w, out_f32=False, keep_trace=keep_trace)
         import torch.distributed as dist
+        if self.pg is None and not dist.is_initialized():
+            raise RuntimeError("W8A8MoE.forward: this rank holds an expert shard but there is no process group to sum the "
+                               "ranks' partial results over; call local_partial() if the partial sum is what you want")
         part = self.local_partial(x, topk_ids, topk_w, out_f32=True, keep_trace=keep_trace)
-        if self.pg is not None or dist.is_initialized():
-            dist.all_reduce(part, group=self.pg)
+        dist.all_reduce(part, group=self.pg)
         return part.to(torch.bfloat16)
 
 

@@ -36,7 +36,8 @@ enum {
     DSV4_ERR_ARG = 1,         /* null pointer, negative size, unsupported stride/alignment */
     DSV4_ERR_LAUNCH = 2,      /* the CUDA runtime rejected the launch */
     DSV4_ERR_DRIVER = 3,      /* tensor-map creation failed / driver entry point missing */
-    DSV4_ERR_DEVICE_WAIT = 4  /* a bounded device-side wait gave up (see dsv4_device_status) */
+    DSV4_ERR_DEVICE_WAIT = 4  /* a bounded wait in an earlier GEMM kernel on this device gave up; returned once by
+                                 the next GEMM launch, which launches nothing (see dsv4_device_status) */
 };
 
 #define DSV4_ABI_VERSION 1
@@ -50,13 +51,16 @@ DSV4_API const char* dsv4_last_error(void);
  * Intended for tests and post-mortems; the launch path never calls it. */
 DSV4_API int dsv4_device_status(dsv4_stream_t stream, int* status_out);
 
-/* Process-wide option, off by default (no reference counterpart).  When enabled, the dense GEMM
+/* Option of the CALLING THREAD, off by default (no reference counterpart): it affects the launches this
+ * thread makes afterwards, on any stream, and nobody else's.  When enabled, the dense GEMM
  * launchers (not the grouped ones) start with programmatic dependent launch: the
  * kernel may begin while the kernel before it on the stream is still running, sets itself up and
  * starts streaming the WEIGHT, and waits for that kernel to complete only before it reads the
  * activations and their scales or writes its output.  The row kernels of this library let such a
  * dependent start as soon as they are running.  Contract when enabled: the weight and its channel
- * scales must not be written by the kernel that directly precedes the GEMM on the stream. */
+ * scales must not be written by the kernel that directly precedes the GEMM on the stream (a weight
+ * update, a dequantisation, a LoRA merge): the GEMM would read them before that kernel has finished,
+ * and nothing reports it. */
 DSV4_API void dsv4_set_overlap_previous_kernel(int enable);
 DSV4_API int dsv4_get_overlap_previous_kernel(void);
 
@@ -143,12 +147,13 @@ DSV4_API int launch_w8a8_gemm_v5(const void* A, const void* B, const void* sa, c
 DSV4_API int launch_w8a8_gemm_ld(const void* A, const void* B, const void* sa, const void* sb, void* C,
                         int64_t ldc, int M, int N, int K, dsv4_stream_t stream);
 
-/* Fused GEMM + all-gather for a column-sharded linear layer.  The tile epilogue stores every
- * 64-byte piece of the result to C_local and, with plain stores over NVLink, to the npeers <= 7
- * buffers in C_peers: host array of DEVICE pointers into the other ranks' output buffers, mapped
- * into this process (CUDA IPC / symmetric memory), each already offset to this rank's column
- * slab; all share the row stride ldc.  N % 32 == 0.  The caller orders the ranks afterwards
- * (a barrier) before anyone reads a full row.  No counterpart in the reference, which has no
+/* Fused GEMM + all-gather for a column-sharded linear layer.  The tile epilogue stages the bf16 tile in
+ * shared memory, 64 columns at a time, and sends every piece with TMA tile stores to C_local and, over
+ * NVLink, to the npeers <= 7 buffers in C_peers (in the order given): host array of DEVICE pointers into
+ * the other ranks' output buffers, mapped into this process (CUDA IPC / symmetric memory), each already
+ * offset to this rank's column slab; all share the row stride ldc.  (Problems too small for the CTA-pair
+ * kernel store 64-byte pieces with plain stores instead.)  N % 32 == 0.  The caller orders the ranks
+ * afterwards (a barrier) before anyone reads a full row.  No counterpart in the reference, which has no
  * collective code. */
 DSV4_API int launch_w8a8_gemm_allgather(const void* A, const void* B, const void* sa, const void* sb,
                                void* C_local, void* const* C_peers, int npeers, int64_t ldc, int M,
