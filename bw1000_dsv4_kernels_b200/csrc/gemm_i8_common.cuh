@@ -53,6 +53,8 @@ struct Params {
     // slab of the other ranks' outputs, mapped into this process); same ldc.  npeers = 0: none.
     void* peerC[7];
     int npeers;
+    // CTA-pair kernel: m-tiles per group of its tile order (see PairTileOrder)
+    int pair_group_m;
     // every bounded wait of the launch gives up after this many nanoseconds
     unsigned long long wait_limit_ns;
     // test hook (never set through the public entry points): the producer issues no tile loads, so

@@ -360,6 +360,16 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
     p.ldc = a.ldc > 0 ? a.ldc : a.N;
     p.sa_groups = a.sa_groups; p.out_i32 = a.out_i32;
     if (p.ldc < a.N) return fail(DSV4_ERR_ARG, "w8a8_gemm: ldc smaller than N");
+    {
+        // groups of m-tiles whose rows of A (256 x K bytes each) take at most 32 MB, all about equally large
+        const int tiles_m = (a.M + 255) / 256;
+        const int64_t tile_bytes = (int64_t)256 * a.K;
+        int gm_max = (int)((int64_t)32 * 1024 * 1024 / (tile_bytes > 0 ? tile_bytes : 1));
+        if (gm_max < 1) gm_max = 1;
+        const int groups = (tiles_m + gm_max - 1) / gm_max;
+        p.pair_group_m = groups > 0 ? (tiles_m + groups - 1) / groups : 1;
+        if (p.pair_group_m < 1) p.pair_group_m = 1;
+    }
     p.npeers = 0;
     for (int d = 0; d < 7; ++d) p.peerC[d] = nullptr;
     if (a.npeers > 0) {
