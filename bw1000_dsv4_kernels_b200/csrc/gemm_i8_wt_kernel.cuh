@@ -25,10 +25,10 @@ namespace {
 //   producer    TMA: weight tile [128 x 128 B] and token tile [N x 128 B] per 128-deep K block
 //               (one tensor map per N = 16, 32, ..., 160, so that no bytes beyond N rows move)
 //   MMA         tcgen05.mma.kind::i8, M128 x N x K32, instruction descriptor built per item
-//   drain       per-token scales (GS = false): whole K accumulates in tensor memory, two
-//               accumulators alternate between items; thread = weight row (output column),
+//   drain       per-token scales (GS = false): whole K accumulates in tensor memory, three
+//               accumulators rotate between items; thread = weight row (output column),
 //               columns = tokens: C[row0 + c, n] = bf16((float(acc) * sa[row0 + c]) * sw[e, n])
-//               group scales (GS = true): every K block is its own accumulator, two alternate;
+//               group scales (GS = true): every K block is its own accumulator, three rotate;
 //               y[c] = fma(float(acc_g[c]), sa[row0 + c, g], y[c]) in registers, sixteen drain
 //               warps (four per lane quarter, the columns dealt round robin eight at a time);
 //               the token scales of each block come from a ring in shared memory that the
@@ -46,7 +46,8 @@ constexpr int kWtWBytes = 128 * BK;
 constexpr int kWtXBytes = kWtChunk * BK;
 constexpr int kWtStageBytes = kWtWBytes + kWtXBytes;
 constexpr int kWtStages = 5;
-constexpr int kWtAccCols = 256;                     // column stride between the two accumulators
+constexpr int kWtAccs = 3;                          // accumulators in tensor memory (3 x 160 of its 512 columns)
+constexpr int kWtAccCols = kWtChunk;                // column stride between them
 
 struct WtMaps {
     CUtensorMap x[kWtMaps];
@@ -60,7 +61,7 @@ struct WtSmem {
     static constexpr int kScaleBytes = 32 * kWtChunk * 4;
     static constexpr int kPrefixOff = kScaleOff + kScaleBytes;
     static constexpr int kBarOff = (kPrefixOff + (kMaxExperts + 1) * 4 + 7) & ~7;
-    static constexpr int kNumBars = 2 * kWtStages + 4;
+    static constexpr int kNumBars = 2 * kWtStages + 2 * kWtAccs;
     static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
     static constexpr int kAbortOff = kTmemSlotOff + 4;
     static constexpr int kTotal = kAbortOff + 4;
@@ -140,17 +141,18 @@ gemm_i8_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
-    auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + kWtAccs + a); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr uint32_t kTmemCols = 2 * kWtAccCols;
+    constexpr uint32_t kTmemCols = 512;
+    static_assert(kWtAccs * kWtAccCols <= 512, "the accumulators fit tensor memory");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(full_bar(s), 1);
             ptx::mbar_init(empty_bar(s), 1);
         }
-        for (int a = 0; a < 2; ++a) {
+        for (int a = 0; a < kWtAccs; ++a) {
             ptx::mbar_init(acc_full_bar(a), 1);
             ptx::mbar_init(acc_empty_bar(a), kDrainWarps);
         }
@@ -249,15 +251,15 @@ gemm_i8_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         if (ptx::elect_one()) {
             int stage = 0;
             uint32_t phase = 0;
-            uint32_t blk = 0;  // accumulator hand-overs so far: buffer = blk & 1, parity = (blk >> 1) & 1
+            uint32_t blk = 0;  // accumulator hand-overs so far: buffer = blk % kWtAccs, parity = (blk / kWtAccs) & 1
             bool ok = true;
             for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
                 const WtItem it = wt_item(p, prefix, tiles_w, t);
                 const uint32_t idesc = ptx::idesc_i8(128, it.nmma);
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     const bool new_acc = GS || kb == 0;
-                    const uint32_t b = blk & 1u;
-                    if (new_acc && (!ptx::mbar_wait_bounded(acc_empty_bar(b), ((blk >> 1) & 1u) ^ 1u, p.wait_limit_ns) ||
+                    const uint32_t b = blk % kWtAccs;
+                    if (new_acc && (!ptx::mbar_wait_bounded(acc_empty_bar(b), ((blk / kWtAccs) & 1u) ^ 1u, p.wait_limit_ns) ||
                                     *abort_flag)) {
                         report_wait_failure(kWaitAccEmpty);
                         *abort_flag = 1;
@@ -307,8 +309,8 @@ gemm_i8_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                 // token scales of the item -> shared memory (everybody reads all of them)
                 asm volatile("bar.sync 1, %0;" ::"n"(kDrain) : "memory");   // the previous item's readers are done
                 for (int i = dtid; i < kWtChunk; i += kDrain) tok_scale[i] = i < it.cnt ? __ldg(p.sa + it.row0 + i) : 0.0f;
-                const uint32_t b = blk & 1u;
-                bool go = ptx::mbar_wait_bounded(acc_full_bar(b), (blk >> 1) & 1u, p.wait_limit_ns) && !*abort_flag;
+                const uint32_t b = blk % kWtAccs;
+                bool go = ptx::mbar_wait_bounded(acc_full_bar(b), (blk / kWtAccs) & 1u, p.wait_limit_ns) && !*abort_flag;
                 go = ptx::barrier_and<1, kDrain>(go);                        // also publishes the scales
                 if (!go) {
                     report_wait_failure(kWaitAccFull);
@@ -360,8 +362,8 @@ gemm_i8_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                 const int npieces = (it.nmma / 8 + 3 - sub) >> 2;
                 bool ok = true;
                 for (int kb = 0; kb < k_blocks; ++kb, ++blk) {
-                    const uint32_t b = blk & 1u;
-                    if (!ptx::mbar_wait_bounded(acc_full_bar(b), (blk >> 1) & 1u, p.wait_limit_ns) || *abort_flag) {
+                    const uint32_t b = blk % kWtAccs;
+                    if (!ptx::mbar_wait_bounded(acc_full_bar(b), (blk / kWtAccs) & 1u, p.wait_limit_ns) || *abort_flag) {
                         report_wait_failure(kWaitAccFull);
                         *abort_flag = 1;
                         ok = false;
