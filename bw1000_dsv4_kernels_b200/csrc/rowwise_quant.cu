@@ -674,12 +674,11 @@ __global__ void __launch_bounds__(1024, 1) silu_mul_quant_async_kernel(
 
     uint32_t it = 0;
     for (int rb = first; rb < nblocks; rb += stride, ++it) {
-        if (!ptx::mbar_wait_bounded(bar, it & 1u)) {
-            atomicCAS(&g_row_status, 0, 201);
-            break;  // every thread of the group times out on the same barrier
-        }
+        // every thread waits for the copies itself; whether the group goes on is decided together at the
+        // first barrier below (a thread whose wait gave up skips its reads and votes no there)
+        const bool arrived = ptx::mbar_wait_bounded(bar, it & 1u);
         const int row = rb * RPB + gi;
-        const bool active = row_active(row);
+        const bool active = arrived && row_active(row);
         const uint4* gb = my_buf + (size_t)(gi * 2) * V;
         const uint4* ub = gb + V;
         // the thread's share of the row block goes to registers first, so that the buffer is free
@@ -697,7 +696,12 @@ __global__ void __launch_bounds__(1024, 1) silu_mul_quant_async_kernel(
                 }
             }
         }
-        group_barrier(1 + grp, GROUP);  // the buffer has been read by everyone
+        // the buffer has been read by everyone -- or somebody's wait gave up, and then the whole group leaves
+        // here, before the named barriers further down
+        if (!ptx::barrier_and_rt(1 + grp, GROUP, arrived)) {
+            atomicCAS(&g_row_status, 0, 201);
+            break;
+        }
         if (gtid == 0 && rb + stride < nblocks) issue(rb + stride);
         float am = 0.0f;
         if (active) {

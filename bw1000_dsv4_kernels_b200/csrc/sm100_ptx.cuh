@@ -72,6 +72,22 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     return false;
 }
 
+// The same with the barrier id and the thread count in registers.
+__device__ __forceinline__ bool barrier_and_rt(int id, int threads, bool pred) {
+    uint32_t out;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.b32 q, %1, 0;\n"
+        "barrier.cta.red.and.pred p, %2, %3, q;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(out)
+        : "r"((uint32_t)pred), "r"(id), "r"(threads)
+        : "memory");
+    return out != 0;
+}
+
 // ---- TMA --------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

@@ -144,6 +144,38 @@ def test_linearity_at_full_size(cabi):
     assert torch.equal(c1[:64, :512].cpu(), ref)
 
 
+def _boundary_indices(size, step=256, halo=2):
+    """Indices either side of every multiple of `step` (tile boundaries), plus both ends."""
+    idx = set(range(0, min(halo, size))) | set(range(max(0, size - halo), size))
+    for b in range(step, size, step):
+        idx |= set(range(b - halo, min(b + halo, size)))
+    return torch.tensor(sorted(idx))
+
+
+@pytest.mark.parametrize("m,n,k", [(2048, 4096, 7168), (2048, 7168, 18432)])
+def test_dense_gemm_full_size_every_tile_boundary(cabi, m, n, k):
+    # the two dense projections at M=2048, at full size.  (1) every int32 accumulator against the library
+    # integer product (a second opinion on all M*N elements); (2) the bf16 result on the rows and columns either
+    # side of EVERY 256-row / 256-column tile boundary of the CTA-pair tiling against the oracle, over the whole
+    # K (first and last K block included)
+    g = torch.Generator(device="cuda").manual_seed(m + n)
+    A = torch.randint(-127, 128, (m, k), dtype=torch.int8, device="cuda", generator=g)
+    B = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda", generator=g)
+    sa = wl.channel_scales((m,), device="cuda", seed=1)
+    sb = wl.channel_scales((n,), device="cuda", seed=2)
+    acc = cabi.w8a8_gemm_i32(A, B)
+    assert torch.equal(acc, torch._int_mm(A, B.t()))
+    out = cabi.w8a8_gemm(A, B, sa, sb)
+    assert cabi.device_status() == 0
+    rows, cols = _boundary_indices(m), _boundary_indices(n)
+    ref = oracle.w8a8_gemm(A[rows.cuda()].cpu(), B[cols.cuda()].cpu(), sa[rows.cuda()].cpu(), sb[cols.cuda()].cpu())
+    got = out[rows.cuda()][:, cols.cuda()].cpu()
+    assert torch.equal(got.contiguous().view(torch.int16), ref.view(torch.int16))
+    # and the whole bf16 result against the formula on the (already checked) accumulators
+    full = ((acc.to(torch.float32) * sa.view(-1, 1)) * sb.view(1, -1)).to(torch.bfloat16)
+    assert torch.equal(out.view(torch.int16), full.view(torch.int16))
+
+
 def test_gemm_argument_errors(cabi, ext):
     A = torch.zeros((4, 24), dtype=torch.int8, device="cuda")
     B = torch.zeros((8, 24), dtype=torch.int8, device="cuda")
@@ -263,6 +295,23 @@ def test_gemm_fused_allgather_tile_store_path(cabi, ext, m, n):
     for b in bufs:
         assert torch.equal(b[:, col0:col0 + n].cpu().view(torch.int16), ref.view(torch.int16))
         assert (b[:, :col0] == 5.0).all() and (b[:, col0 + n:] == 5.0).all()
+
+
+def test_gemm_fused_allgather_eight_destinations(cabi, ext):
+    # the widest case the entry point takes: this rank's buffer and seven peers (eight tensor maps of stores),
+    # emulated with eight local buffers; the destinations are written in the order given
+    m, n, k, width, col0 = 2048, 2560, 256, 3072, 512
+    A, B, sa, sb = _operands(m, n, k, seed=77)
+    ref = oracle.w8a8_gemm(A, B, sa, sb)
+    bufs = [torch.full((m, width), 5.0, dtype=torch.bfloat16, device="cuda") for _ in range(8)]
+    order = [3, 4, 5, 6, 7, 1, 2]      # a rotated peer order, as a rank in the middle would pass it
+    ext.w8a8_gemm_allgather(A.cuda(), B.cuda(), sa.cuda(), sb.cuda(), bufs[0], col0, [bufs[i].data_ptr() for i in order])
+    assert cabi.device_status() == 0
+    for b in bufs:
+        assert torch.equal(b[:, col0:col0 + n].cpu().view(torch.int16), ref.view(torch.int16))
+        assert (b[:, :col0] == 5.0).all() and (b[:, col0 + n:] == 5.0).all()
+    with pytest.raises(RuntimeError):   # an eighth peer is one too many
+        ext.w8a8_gemm_allgather(A.cuda(), B.cuda(), sa.cuda(), sb.cuda(), bufs[0], col0, [b.data_ptr() for b in bufs])
 
 
 def test_tp_linear_full_size_shards_equal_the_whole(ext):
