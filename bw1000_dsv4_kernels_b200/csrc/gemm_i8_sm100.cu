@@ -84,7 +84,33 @@ EncodeTiledFn encode_tiled_fn() {
 
 // 2-D uint8 tensor [rows, K] (K contiguous), box = 128 bytes of K x box_rows rows,
 // 128-byte swizzle, out-of-range elements read as zero.
+// Encoded tensor maps are kept per thread in a small table keyed by everything that goes into them (a
+// descriptor holds an address and a shape, nothing that can go stale): a serving loop launches the same few
+// GEMMs over the same buffers, and the grouped GEMM alone needs eleven maps per launch.
+struct TileMapKey {
+    const void* base;
+    uint64_t rows, K;
+    uint32_t box_rows;
+    bool operator==(const TileMapKey& o) const {
+        return base == o.base && rows == o.rows && K == o.K && box_rows == o.box_rows;
+    }
+};
+struct TileMapCache {
+    static constexpr int kEntries = 64;
+    TileMapKey key[kEntries];
+    CUtensorMap map[kEntries];
+    int used = 0, next = 0;
+};
+
 int make_tile_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+    static thread_local TileMapCache cache;
+    const TileMapKey k{base, rows, K, box_rows};
+    for (int i = 0; i < cache.used; ++i) {
+        if (cache.key[i] == k) {
+            *map = cache.map[i];
+            return 0;
+        }
+    }
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return fail(DSV4_ERR_DRIVER, "w8a8_gemm: cuTensorMapEncodeTiled is not available");
     const cuuint64_t dims[2] = {K, rows};
@@ -100,6 +126,10 @@ int make_tile_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K,
                  (int)r, (unsigned long long)rows, (unsigned long long)K);
         return fail(DSV4_ERR_DRIVER, msg);
     }
+    const int slot = cache.used < TileMapCache::kEntries ? cache.used++ : cache.next;
+    cache.next = (slot + 1) % TileMapCache::kEntries;
+    cache.key[slot] = k;
+    cache.map[slot] = *map;
     return 0;
 }
 

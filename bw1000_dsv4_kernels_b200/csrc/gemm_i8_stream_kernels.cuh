@@ -12,12 +12,16 @@ namespace {
 // rows] int32, one in each peer CTA's shared memory, fixed order r = 0..S-1), applies the scales and
 // stores.  Work item = (token column c, group of four weight rows): 16-byte loads through
 // distributed shared memory, four outputs that are contiguous in C; consecutive threads take
-// consecutive row groups of one column.  Four items are in flight per thread, because one item at a
-// time would cost a full remote-load latency per item.
-template <int MAXS>
+// consecutive row groups of one column.  U items are in flight per thread (four with up to eight
+// partials, eight with up to four), because one item at a time would cost a full remote-load latency
+// per item; measured, a remote read costs about a microsecond and moves about 25 GB/s per SM, and a
+// bulk reduce-add into the owner's shared memory (tried instead of these loads) is no faster.  The
+// token and channel scales were put into shared memory (sa_s[token], sb_s[row in tile]) while the
+// weight streamed, so that no global-memory latency follows the remote loads.
+template <int MAXS, int U>
 __device__ __forceinline__ void reduce_partials_and_store(const Params& p, const uint32_t (&peer_base)[MAXS], int S,
-                                                          int cols_lo, int cols_hi, int n0, int tid, int nthreads) {
-    constexpr int U = 4;
+                                                          int cols_lo, int cols_hi, int n0, int tid, int nthreads,
+                                                          const float* sa_s, const float* sb_s) {
     const bool vec_store = p.out_i32 ? ((p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0))
                                      : ((p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 7) == 0));
     const int items = (cols_hi - cols_lo) * 32;
@@ -58,10 +62,9 @@ __device__ __forceinline__ void reduce_partials_and_store(const Params& p, const
                         if (n + j < p.N) out[j] = v4[j];
                 }
             } else {
-                const float sa = __ldg(p.sa + c);
-                float sbv[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) sbv[j] = (n + j < p.N) ? __ldg(p.sb + n + j) : 0.0f;
+                const float sa = sa_s[c];
+                const float4 sb4 = *reinterpret_cast<const float4*>(sb_s + g * 4);
+                const float sbv[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
                 const uint32_t lo = pack_bf16x2_rn(__fmul_rn(__fmul_rn(__int2float_rn(a0), sa), sbv[0]),
                                                    __fmul_rn(__fmul_rn(__int2float_rn(a1), sa), sbv[1]));
                 const uint32_t hi = pack_bf16x2_rn(__fmul_rn(__fmul_rn(__int2float_rn(a2), sa), sbv[2]),
@@ -104,13 +107,24 @@ struct StreamSmem {
     static constexpr int kTilesBytes = kStages * kStageBytes;
     static constexpr int kPartialBytes = NTOK * 128 * 4;
     static_assert(kPartialBytes <= kTilesBytes, "the partial tile reuses the stage ring");
-    static constexpr int kBarOff = kTilesBytes;
+    static constexpr int kScaleOff = kTilesBytes;             // token scales [256], then the tile's 128 channel scales
+    static constexpr int kBarOff = kScaleOff + (256 + 128) * 4;
     static constexpr int kNumBars = 2 * kStages + 1;
     static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
     static constexpr int kAbortOff = kTmemSlotOff + 4;
     static constexpr int kTotal = kAbortOff + 4;
     static constexpr int kDynamic = kTotal + 1024;
 };
+
+// The drain warps (threads 64..191) have nothing to do while the weight streams: they fetch the scales the
+// epilogue needs.  Activation scales may come from the kernel before this one, hence the dependency wait.
+__device__ __forceinline__ void stage_scales(const Params& p, float* sa_s, float* sb_s, int ntok, int n0) {
+    ptx::grid_dependency_wait();
+    if (p.out_i32) return;
+    const int t = threadIdx.x - 64;
+    for (int i = t; i < ntok; i += kDrainThreads) sa_s[i] = i < p.M ? __ldg(p.sa + i) : 0.0f;
+    for (int j = t; j < 128; j += kDrainThreads) sb_s[j] = n0 + j < p.N ? __ldg(p.sb + n0 + j) : 0.0f;
+}
 
 template <int NTOK>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -124,6 +138,8 @@ gemm_i8_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlotOff);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
     int* partial = reinterpret_cast<int*>(smem);  // [NTOK][128] once the ring has drained
+    float* sa_s = reinterpret_cast<float*>(smem + L::kScaleOff);
+    float* sb_s = sa_s + 256;
 
     const uint32_t tiles_base = ptx::smem_u32(smem);
     const uint32_t bar_base = ptx::smem_u32(bars);
@@ -219,7 +235,8 @@ gemm_i8_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             if (issued_all) ptx::tc_commit(acc_full_bar);
         }
     } else {
-        // drain warps: accumulator -> shared partial (or straight out when K is not split)
+        // drain warps: the epilogue's scales first, then accumulator -> shared partial
+        stage_scales(p, sa_s, sb_s, NTOK, n0);
         const int quarter = warp & 3;
         const int wrow = quarter * 32 + lane;  // weight row inside the tile = TMEM lane
         if (kb1 > kb0) {
@@ -274,7 +291,7 @@ gemm_i8_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         uint32_t peer_base[8];
 #pragma unroll
         for (int r = 0; r < 8; ++r) peer_base[r] = ptx::map_to_cta(my_partial, r < S ? r : 0);
-        reduce_partials_and_store<8>(p, peer_base, S, cols_lo, cols_hi, n0, threadIdx.x, kThreads);
+        reduce_partials_and_store<8, 4>(p, peer_base, S, cols_lo, cols_hi, n0, threadIdx.x, kThreads, sa_s, sb_s);
     }
 
     // nobody leaves while a peer may still read its shared memory
@@ -305,7 +322,8 @@ struct StreamPairSmem {
     static constexpr int kTilesBytes = kStages * kStageBytes;
     static constexpr int kPartialBytes = 256 * 128 * 4;
     static_assert(kPartialBytes <= kTilesBytes, "the partial tile reuses the stage ring");
-    static constexpr int kBarOff = kTilesBytes;
+    static constexpr int kScaleOff = kTilesBytes;             // token scales [256], then the tile's 128 channel scales
+    static constexpr int kBarOff = kScaleOff + (256 + 128) * 4;
     static constexpr int kNumBars = 2 * kStages + 1;
     static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
     static constexpr int kAbortOff = kTmemSlotOff + 4;
@@ -324,6 +342,8 @@ gemm_i8_stream_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlotOff);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
     int* partial = reinterpret_cast<int*>(smem);  // [NTOK][128] once the ring has drained
+    float* sa_s = reinterpret_cast<float*>(smem + L::kScaleOff);
+    float* sb_s = sa_s + 256;
 
     const uint32_t tiles_base = ptx::smem_u32(smem);
     const uint32_t bar_base = ptx::smem_u32(bars);
@@ -424,7 +444,9 @@ gemm_i8_stream_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
             if (issued_all) ptx::tc_commit_pair(acc_full_bar, pair_mask);
         }
     } else {
-        // drain warps of both CTAs: accumulator of this CTA's 128 weight rows -> shared partial
+        // drain warps of both CTAs: the epilogue's scales first, then the accumulator of this CTA's 128 weight
+        // rows -> shared partial
+        stage_scales(p, sa_s, sb_s, NTOK, n0);
         const int quarter = warp & 3;
         const int wrow = quarter * 32 + lane;
         if (kb1 > kb0) {
@@ -468,7 +490,7 @@ gemm_i8_stream_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
         uint32_t peer_base[4];
 #pragma unroll
         for (int r = 0; r < 4; ++r) peer_base[r] = ptx::map_to_cta(my_partial, (uint32_t)(2 * (r < S ? r : 0) + half));
-        reduce_partials_and_store<4>(p, peer_base, S, cols_lo, cols_hi, n0, threadIdx.x, kThreads);
+        reduce_partials_and_store<4, 8>(p, peer_base, S, cols_lo, cols_hi, n0, threadIdx.x, kThreads, sa_s, sb_s);
     }
 
     // nobody leaves while a peer may still read its shared memory

@@ -208,6 +208,35 @@ def test_grouped_gemm_is_per_segment_dense_gemm():
     assert (out_g[lo:hi].float() - y.float()).abs().max().item() <= 0.01 * y.abs().max().item()
 
 
+def test_masked_layout_oracle_equals_the_row_list_forms():
+    # the masked expert layout ([E, max_m, .] blocks, masked_m[e] valid rows each) is a re-indexing of the
+    # sorted-segment / per-row-flag forms: same rows in, same bits out, every other row untouched
+    e, max_m, n, k = 4, 12, 24, 256
+    counts = [0, 12, 5, 40]          # 40 > max_m counts as max_m
+    A = wl.int8_weights((e, max_m, k), seed=1)
+    W = wl.int8_weights((e, n, k), seed=2)
+    sw = wl.channel_scales((e, n), seed=4)
+    mm = torch.tensor(counts, dtype=torch.int32)
+    valid = [min(c, max_m) for c in counts]
+    rows = torch.cat([torch.arange(c) + i * max_m for i, c in enumerate(valid)])
+    off = torch.tensor([0] + list(torch.cumsum(torch.tensor(valid), 0)), dtype=torch.int32)
+    for sa in (wl.channel_scales((e, max_m), seed=3), wl.channel_scales((e, max_m, k // 128), seed=3)):
+        out = oracle.grouped_gemm_masked(A, W, sa, sw, mm, out=torch.full((e, max_m, n), 3.0, dtype=torch.bfloat16))
+        sa_rows = sa.reshape(e * max_m, -1)[rows]
+        ref = oracle.grouped_gemm(A.view(-1, k)[rows], W, sa_rows.reshape(-1) if sa.dim() == 2 else sa_rows, sw, off)
+        assert torch.equal(bits(out.view(-1, n)[rows]), bits(ref))
+        untouched = torch.ones(e * max_m, dtype=torch.bool)
+        untouched[rows] = False
+        assert (out.view(-1, n)[untouched] == 3.0).all()
+    flags = oracle.masked_row_flags(mm, max_m)
+    assert flags.tolist() == [0] * 12 + [1] * 12 + [1] * 5 + [0] * 7 + [1] * 12
+    gu = wl.randn_bf16((e, max_m, 2 * n), seed=5)
+    q, s = oracle.silu_and_mul_masked_post_quant(gu[..., :n], gu[..., n:], mm)
+    q_ref, s_ref = oracle.silu_mul_quant(gu.view(-1, 2 * n)[rows][:, :n], gu.view(-1, 2 * n)[rows][:, n:])
+    assert torch.equal(q.view(-1, n)[rows], q_ref) and torch.equal(s.view(-1, 1)[rows], s_ref)
+    assert q.view(-1, n)[untouched].abs().sum().item() == 0 and s.view(-1)[untouched].abs().sum().item() == 0
+
+
 def test_moe_segments_oracle():
     ids, _ = wl.moe_routing(100, 16, 4, seed=0)
     off, src, dst = oracle.moe_segments(ids, 16)
