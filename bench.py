@@ -727,7 +727,7 @@ def run_ours(args):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of gemm_i8_pair_kernel at M=8192 N=28672 K=7168
 # (profiles/gemm_i8_pair_kernel_M8192_N28672_K7168.md)
-GEMM_TP_TRAFFIC_BYTES = 527967232 + 448902400
+GEMM_TP_TRAFFIC_BYTES = 513608704 + 448874752
 
 
 def run_single_kernel(args):
