@@ -283,7 +283,7 @@ int launch_stream_pair(const CUtensorMap& tmW, const CUtensorMap& tmX, const Par
 // Grouped GEMM, weights on the MMA's M axis: one CTA per SM walks the (expert, token chunk, weight tile) items.
 template <bool GS>
 int launch_wt_variant(const CUtensorMap& tmW, const WtMaps& xmaps, const Params& p, cudaStream_t st) {
-    using L = WtSmem;
+    using L = WtSmem<GS>;
     static_assert(L::kDynamic <= 227 * 1024, "shared memory limit");
     static bool opted_in[64] = {};
     if (!opt_in_shared_memory(gemm_i8_wt_kernel<GS>, L::kDynamic, opted_in))

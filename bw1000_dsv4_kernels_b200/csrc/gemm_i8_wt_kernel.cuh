@@ -45,7 +45,6 @@ constexpr int kWtMaps = kWtChunk / 16;              // token tensor maps: box ro
 constexpr int kWtWBytes = 128 * BK;
 constexpr int kWtXBytes = kWtChunk * BK;
 constexpr int kWtStageBytes = kWtWBytes + kWtXBytes;
-constexpr int kWtStages = 5;
 constexpr int kWtAccs = 3;                          // accumulators in tensor memory (3 x 160 of its 512 columns)
 constexpr int kWtAccCols = kWtChunk;                // column stride between them
 
@@ -53,15 +52,19 @@ struct WtMaps {
     CUtensorMap x[kWtMaps];
 };
 
+template <bool GS>
 struct WtSmem {
-    static constexpr int kTilesBytes = kWtStages * kWtStageBytes;
+    // how far the weight stream runs ahead decides the HBM rate (four stages 395 us, five 345, six 328 on 64
+    // experts of 136 rows); with group scales the scale ring takes the room of the sixth stage
+    static constexpr int kStages = GS ? 5 : 6;
+    static constexpr int kTilesBytes = kStages * kWtStageBytes;
     // token scales: [160] (per-token scales) or, for group scales, a ring of 32 K blocks x 160 tokens that the
-    // producer warp fills (it runs at most STAGES + 2 + 4 blocks ahead of the slowest reader)
+    // producer warp fills (it runs at most kStages + 2 + 4 blocks ahead of the slowest reader)
     static constexpr int kScaleOff = kTilesBytes;
-    static constexpr int kScaleBytes = 32 * kWtChunk * 4;
+    static constexpr int kScaleBytes = (GS ? 32 : 1) * kWtChunk * 4;
     static constexpr int kPrefixOff = kScaleOff + kScaleBytes;
     static constexpr int kBarOff = (kPrefixOff + (kMaxExperts + 1) * 4 + 7) & ~7;
-    static constexpr int kNumBars = 2 * kWtStages + 2 * kWtAccs;
+    static constexpr int kNumBars = 2 * kStages + 2 * kWtAccs;
     static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
     static constexpr int kAbortOff = kTmemSlotOff + 4;
     static constexpr int kTotal = kAbortOff + 4;
@@ -124,8 +127,8 @@ __device__ __forceinline__ WtItem wt_item(const Params& p, const int* prefix, in
 template <bool GS>
 __global__ void __launch_bounds__(GS ? 576 : 192, 1)
 gemm_i8_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ WtMaps xmaps, const Params p) {
-    using L = WtSmem;
-    constexpr int STAGES = kWtStages;
+    using L = WtSmem<GS>;
+    constexpr int STAGES = L::kStages;
     constexpr int kDrainWarps = GS ? 16 : 4;
     constexpr int kDrain = kDrainWarps * 32;
     extern __shared__ uint8_t smem_raw[];
