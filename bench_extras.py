@@ -54,6 +54,19 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launch
 
     K, N1, I, H = wl.HIDDEN, wl.DENSE_N, wl.DENSE_INTER, wl.HIDDEN
 
+    def copy_same_bytes(entry):
+        """Context for an HBM-bound entry: a library device-to-device copy that moves the same total bytes
+        (half read, half written), over rotating buffers and timed the same way.  How far below the peak a
+        copy of this size sits is what launch, ramp and tail cost at this size."""
+        half = max(1 << 20, entry["bytes"] // 2)
+        n = max(2, rotation_count(2 * half))
+        src = [torch.empty(half, dtype=torch.uint8, device=dev).random_(0, 255) for _ in range(n)]
+        dst = [torch.empty(half, dtype=torch.uint8, device=dev) for _ in range(n)]
+        us = 1e3 * time_launches_graph(lambda i: dst[i % n].copy_(src[i % n]))
+        entry["copy_same_bytes_us"] = round(us, 3)
+        entry["frac_of_copy_same_bytes"] = round(us / entry["us"], 4)
+        return entry
+
     # ---- per_token_quant_int8 ------------------------------------------------------------
     sec = {}
     for m in (64, 2048, 8192):
@@ -63,6 +76,8 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launch
         us, lp = both(_hold(lambda i: ext.per_token_quant_int8(xs[i % n]), n))
         sec[f"M={m}"] = _entry(us, peaks, bytes_=3 * m * K + 4 * m, us_host_loop=lp)
         del xs
+        if m >= 2048:
+            copy_same_bytes(sec[f"M={m}"])
     res["per_token_quant_int8 K=7168"] = sec
 
     # ---- per_token_group_quant_int8 ------------------------------------------------------
@@ -73,6 +88,7 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launch
         us, lp = both(_hold(lambda i: ext.per_token_group_quant_int8(xs[i % n], 128), n))
         sec[f"M={m}"] = _entry(us, peaks, bytes_=3 * m * K + 4 * m * (K // 128), us_host_loop=lp)
         del xs
+        copy_same_bytes(sec[f"M={m}"])
     res["per_token_group_quant_int8 K=7168 gs=128"] = sec
 
     # ---- add_rmsnorm_quant -> w8a8_gemm --------------------------------------------------
@@ -89,6 +105,8 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launch
         rs = [wl.randn_bf16((m, K), device=dev, seed=100 + i) for i in range(n)]
         us, lp = both(_hold(lambda i: ext.add_rmsnorm_quant(rs[i % n], xs[i % n], gamma, 1e-6), n))
         quant_sec[f"M={m}"] = _entry(us, peaks, bytes_=m * (7 * K + 4) + 2 * K, us_host_loop=lp)
+        if m >= 2048:
+            copy_same_bytes(quant_sec[f"M={m}"])
         qs = [ext.add_rmsnorm_quant(rs[i], xs[i], gamma, 1e-6) for i in range(min(n, 5))]
         nq = len(qs)
         us, lp = both(lambda i: ext.w8a8_scaled_gemm(qs[i % nq][0], w_sets[i % NW], qs[i % nq][1], w_scale))
@@ -147,6 +165,8 @@ def run(ext, dev, rank, world, peaks, time_launches, rotation_count, time_launch
         silu_sec[f"M={m}"] = _entry(us, peaks, bytes_=m * (5 * I + 4), us_host_loop=lp)
         q, s = ext.silu_mul_quant(gus[0][:, :I], gus[0][:, I:])
         del gus
+        if m == 2048:
+            copy_same_bytes(silu_sec[f"M={m}"])
         us, lp = both(lambda i: ext.w8a8_scaled_gemm(q, wd_sets[i % 2], s, wd_scale), _iters(150 if m > 64 else 30))
         down_sec[f"M={m}"] = _entry(us, peaks, bytes_=m * I + H * I + 2 * m * H + 4 * (m + H), ops=2.0 * m * H * I,
                                     us_host_loop=lp)
