@@ -265,9 +265,20 @@ def _moe_section(ext, dev, rank, world, peaks, timer, time_launches_graph):
                 sec["TOPS_whole_job"] = round(ops / (t_ex["ms"] * 1e-3) / 1e12, 1)
                 y = ex.forward(inp.x, inp.topk_ids, inp.topk_w).clone()
                 del ex
+                # the down GEMM stores every row into the inbox of the token's owner; the combine reads local memory
+                push = moe.PushExchangeW8A8MoE(inp.w13, inp.w13_scale, inp.w2, inp.w2_scale, E, rank, world, t_max=T,
+                                               topk=topk, device=dev, group_scaled=gs)
+                t_push = med(lambda i: push.forward(inp.x, inp.topk_ids, inp.topk_w))
+                sec["with_rows_pushed_by_down_gemm"] = t_push
+                y_push = push.forward(inp.x, inp.topk_ids, inp.topk_w).clone()
+                torch.cuda.synchronize()
+                sec["pushed_rows_equal_fused_exchange"] = bool(torch.equal(y_push.view(torch.int16), y.view(torch.int16)))
+                if t_push["ms"] < t_ex["ms"]:
+                    sec["TOPS_whole_job"] = round(ops / (t_push["ms"] * 1e-3) / 1e12, 1)
+                del push
             except Exception as exc:  # pragma: no cover
                 sec["fused_exchange_error"] = f"{type(exc).__name__}: {exc}"
-                sec["TOPS_whole_job"] = round(ops / (t_ar["ms"] * 1e-3) / 1e12, 1)
+                sec.setdefault("TOPS_whole_job", round(ops / (t_ar["ms"] * 1e-3) / 1e12, 1))
         if y is not None:
             # parity inside the run: a few of this rank's tokens against the one-GPU chain recomputed here
             t0, t1 = moe.token_range(rank, world, T)

@@ -211,6 +211,22 @@ int launch_grouped_gemm(const void* A, const void* W, const void* sa, const void
     return gemm_i8(a, cs(stream));
 }
 
+int launch_grouped_gemm_scatter(const void* A, const void* W, const void* sa, const void* sw, const int* expert_offsets,
+                                void* const* row_ptr, int R, int E, int N, int K, dsv4_stream_t stream) {
+    if (expert_offsets == nullptr) return fail(DSV4_ERR_ARG, "grouped_gemm_scatter: null pointer expert_offsets");
+    if (row_ptr == nullptr) return fail(DSV4_ERR_ARG, "grouped_gemm_scatter: null pointer row_ptr");
+    GemmArgs a{};
+    a.A = A; a.B = W; a.sa = static_cast<const float*>(sa); a.sb = static_cast<const float*>(sw); a.C = nullptr;
+    a.row_ptr = row_ptr;
+    a.offsets = expert_offsets; a.M = R; a.N = N; a.K = K; a.E = E; a.sa_groups = 1; a.out_i32 = 0;
+    return gemm_i8(a, cs(stream));
+}
+
+int launch_moe_push_rows(const int* dst_slot, int T, int topk, int tokens_per_rank, void* const* inbox_ranks,
+                         int num_ranks, int H, void** row_ptr, dsv4_stream_t stream) {
+    return moe_push_rows(dst_slot, T, topk, tokens_per_rank, inbox_ranks, num_ranks, H, row_ptr, cs(stream));
+}
+
 int launch_grouped_gemm_masked(const void* A, const void* W, const void* sa, const void* sw, const int* masked_m,
                                void* C, int E, int max_m, int N, int K, int sa_groups, dsv4_stream_t stream) {
     if (masked_m == nullptr) return fail(DSV4_ERR_ARG, "grouped_gemm_masked: null pointer masked_m");

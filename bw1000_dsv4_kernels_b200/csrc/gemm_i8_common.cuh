@@ -55,6 +55,9 @@ struct Params {
     int npeers;
     // CTA-pair kernel: m-tiles per group of its tile order (see PairTileOrder)
     int pair_group_m;
+    // grouped GEMM with per-token scales only: row r of the result goes to row_ptr[r] (a bf16 row of N elements,
+    // possibly in another GPU's memory) instead of C + r * ldc; null = C
+    void* const* row_ptr;
     // every bounded wait of the launch gives up after this many nanoseconds
     unsigned long long wait_limit_ns;
     // test hook (never set through the public entry points): the producer issues no tile loads, so

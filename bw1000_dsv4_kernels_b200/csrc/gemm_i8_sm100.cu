@@ -281,12 +281,12 @@ int launch_stream_pair(const CUtensorMap& tmW, const CUtensorMap& tmX, const Par
 }
 
 // Grouped GEMM, weights on the MMA's M axis: one CTA per SM walks the (expert, token chunk, weight tile) items.
-template <bool GS>
+template <bool GS, bool STAGED = false>
 int launch_wt_variant(const CUtensorMap& tmW, const WtMaps& xmaps, const Params& p, cudaStream_t st) {
-    using L = WtSmem<GS>;
+    using L = WtSmem<GS, STAGED>;
     static_assert(L::kDynamic <= 227 * 1024, "shared memory limit");
     static bool opted_in[64] = {};
-    if (!opt_in_shared_memory(gemm_i8_wt_kernel<GS>, L::kDynamic, opted_in))
+    if (!opt_in_shared_memory(gemm_i8_wt_kernel<GS, STAGED>, L::kDynamic, opted_in))
         return fail(DSV4_ERR_LAUNCH, "grouped_gemm: cannot raise the dynamic shared memory limit");
     int grid = sm_count();
     if (grid <= 0) return fail(DSV4_ERR_LAUNCH, "grouped_gemm: no CUDA device");
@@ -294,7 +294,7 @@ int launch_wt_variant(const CUtensorMap& tmW, const WtMaps& xmaps, const Params&
     const int64_t bound = ((int64_t)p.M / kWtChunk + p.E) * ((p.N + 127) / 128);
     if (bound < grid) grid = (int)bound;
     if (grid < 1) grid = 1;
-    gemm_i8_wt_kernel<GS><<<grid, GS ? 576 : 192, L::kDynamic, st>>>(tmW, xmaps, p);
+    gemm_i8_wt_kernel<GS, STAGED><<<grid, GS ? 576 : 192, L::kDynamic, st>>>(tmW, xmaps, p);
     return check_launch("grouped_gemm");
 }
 
@@ -356,7 +356,10 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
     if (a.M < 0 || a.N < 0 || a.K < 0) return fail(DSV4_ERR_ARG, "w8a8_gemm: negative size");
     if (a.M == 0 || a.N == 0) return 0;
     if (a.K == 0) return fail(DSV4_ERR_ARG, "w8a8_gemm: K must be positive");
-    if (a.A == nullptr || a.B == nullptr || a.C == nullptr) return fail(DSV4_ERR_ARG, "w8a8_gemm: null pointer");
+    if (a.A == nullptr || a.B == nullptr || (a.C == nullptr && a.row_ptr == nullptr))
+        return fail(DSV4_ERR_ARG, "w8a8_gemm: null pointer");
+    if (a.row_ptr != nullptr && (!grouped || a.sa_groups != 1 || a.out_i32 || a.npeers != 0))
+        return fail(DSV4_ERR_ARG, "grouped_gemm_scatter: row destinations exist only for the grouped GEMM with per-token scales");
     if (!a.out_i32 && (a.sa == nullptr || a.sb == nullptr)) return fail(DSV4_ERR_ARG, "w8a8_gemm: null scale pointer");
     if (a.K % 16 != 0) return fail(DSV4_ERR_ARG, "w8a8_gemm: K must be a multiple of 16 (TMA row stride)");
     if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15))
@@ -386,6 +389,7 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
     p.withhold_loads = a.test_withhold_loads;
     p.sa = a.sa; p.sb = a.sb; p.C = a.C; p.offsets = a.offsets;
     p.masked_m = a.masked_m; p.max_m = a.max_m;
+    p.row_ptr = a.row_ptr;
     p.M = a.M; p.N = a.N; p.K = a.K; p.E = grouped ? a.E : 1;
     p.ldc = a.ldc > 0 ? a.ldc : a.N;
     p.sa_groups = a.sa_groups; p.out_i32 = a.out_i32;
@@ -438,6 +442,7 @@ int gemm_i8(const GemmArgs& a, cudaStream_t st) {
             rcw = make_tile_map(&xmaps.x[i], a.A, (uint64_t)a.M, (uint64_t)a.K, (uint32_t)(16 * (i + 1)));
             if (rcw) return rcw;
         }
+        if (a.row_ptr != nullptr) return launch_wt_variant<false, true>(tmB, xmaps, p, st);
         return a.sa_groups != 1 ? launch_wt_variant<true>(tmB, xmaps, p, st) : launch_wt_variant<false>(tmB, xmaps, p, st);
     }
     // Few tokens: stream the weight once, tokens on the MMA's N axis, K split over a cluster

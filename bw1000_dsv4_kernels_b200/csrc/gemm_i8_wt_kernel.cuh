@@ -52,17 +52,20 @@ struct WtMaps {
     CUtensorMap x[kWtMaps];
 };
 
-template <bool GS>
+template <bool GS, bool STAGED = false>
 struct WtSmem {
     // how far the weight stream runs ahead decides the HBM rate (four stages 395 us, five 345, six 328 on 64
     // experts of 136 rows); with group scales the scale ring takes the room of the sixth stage
-    static constexpr int kStages = GS ? 5 : 6;
+    static constexpr int kStages = (GS || STAGED) ? 5 : 6;   // STAGED: the sixth stage's room holds the output tile
     static constexpr int kTilesBytes = kStages * kWtStageBytes;
     // token scales: [160] (per-token scales) or, for group scales, a ring of 32 K blocks x 160 tokens that the
     // producer warp fills (it runs at most kStages + 2 + 4 blocks ahead of the slowest reader)
     static constexpr int kScaleOff = kTilesBytes;
     static constexpr int kScaleBytes = (GS ? 32 : 1) * kWtChunk * 4;
-    static constexpr int kPrefixOff = kScaleOff + kScaleBytes;
+    // STAGED: bf16 [160 tokens][128 weight rows], the item's result before it leaves in 256-byte row segments
+    static constexpr int kOutOff = kScaleOff + kScaleBytes;
+    static constexpr int kOutBytes = STAGED ? kWtChunk * 128 * 2 : 0;
+    static constexpr int kPrefixOff = kOutOff + kOutBytes;
     static constexpr int kBarOff = (kPrefixOff + (kMaxExperts + 1) * 4 + 7) & ~7;
     static constexpr int kNumBars = 2 * kStages + 2 * kWtAccs;
     static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
@@ -124,16 +127,18 @@ __device__ __forceinline__ WtItem wt_item(const Params& p, const int* prefix, in
     return it;
 }
 
-template <bool GS>
+template <bool GS, bool STAGED = false>
 __global__ void __launch_bounds__(GS ? 576 : 192, 1)
 gemm_i8_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ WtMaps xmaps, const Params p) {
-    using L = WtSmem<GS>;
+    static_assert(!(GS && STAGED), "row destinations go with per-token scales");
+    using L = WtSmem<GS, STAGED>;
     constexpr int STAGES = L::kStages;
     constexpr int kDrainWarps = GS ? 16 : 4;
     constexpr int kDrain = kDrainWarps * 32;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     float* tok_scale = reinterpret_cast<float*>(smem + L::kScaleOff);
+    __nv_bfloat16* out_tile = reinterpret_cast<__nv_bfloat16*>(smem + L::kOutOff);   // STAGED only
     int* prefix = reinterpret_cast<int*>(smem + L::kPrefixOff);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlotOff);
@@ -334,7 +339,7 @@ gemm_i8_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(acc_empty_bar(b));
                     }
-                    if (!n_ok) continue;
+                    if (!STAGED && !n_ok) continue;
 #pragma unroll
                     for (int j4 = 0; j4 < 4; ++j4) {
                         const float4 s4 = *reinterpret_cast<const float4*>(tok_scale + c0 + 4 * j4);
@@ -344,8 +349,33 @@ gemm_i8_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                             const int c = c0 + 4 * j4 + j;
                             if (c < it.cnt) {
                                 const float v = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * j4 + j]), sv[j]), sbn);
-                                out[(int64_t)c * p.ldc] = __float2bfloat16_rn(v);
+                                if constexpr (STAGED)
+                                    out_tile[c * 128 + wrow] = __float2bfloat16_rn(v);
+                                else
+                                    out[(int64_t)c * p.ldc] = __float2bfloat16_rn(v);
                             }
+                        }
+                    }
+                }
+                if constexpr (STAGED) {
+                    // The item's tile [tokens][128 weight rows] is in shared memory: every token's 256 bytes leave as
+                    // sixteen 16-byte stores of neighbouring lanes, to the row's own destination (a remote store of
+                    // 64 bytes, what a warp's 2-byte stores of one token amount to, uses a fraction of an NVLink
+                    // packet).  The barrier at the top of the next item keeps the tile until everybody has read it.
+                    asm volatile("bar.sync 2, %0;" ::"n"(kDrain) : "memory");
+                    const int seg = dtid & 15;                       // 16-byte piece of the 256-byte row segment
+                    const int nn = it.n0 + seg * 8;
+                    for (int c = dtid >> 4; c < it.cnt; c += kDrain / 16) {
+                        __nv_bfloat16* dst = p.row_ptr != nullptr
+                            ? reinterpret_cast<__nv_bfloat16*>(__ldg(reinterpret_cast<const unsigned long long*>(p.row_ptr) + it.row0 + c))
+                            : static_cast<__nv_bfloat16*>(p.C) + (int64_t)(it.row0 + c) * p.ldc;
+                        const uint4 v = *reinterpret_cast<const uint4*>(out_tile + c * 128 + seg * 8);
+                        if (nn + 8 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+                            *reinterpret_cast<uint4*>(dst + nn) = v;
+                        } else {
+                            const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+                            for (int j = 0; j < 8; ++j)
+                                if (nn + j < p.N) dst[nn + j] = e[j];
                         }
                     }
                 }

@@ -39,6 +39,7 @@ struct GemmArgs {
     int64_t ldc;          // row stride of C in elements; 0 = N
     int sa_groups;        // 1 = per-token scale; K/128 = one scale per 128 of K
     int out_i32;          // 1 = write raw int32 accumulators
+    void* const* row_ptr = nullptr;  // grouped GEMM, per-token scales: device array, one destination row per result row (C unused)
     void* peerC[7];       // fused all-gather: the other ranks' mapped output slabs
     int npeers;           // 0 = none
     // Test hook, zero through every public entry point: the tile producers of the launch issue no
@@ -64,6 +65,8 @@ int overlap_previous_kernel();
 int moe_combine_exchange(const void* const* z_ranks, const int* const* slot_ranks, const int* topk_ids,
                          const float* topk_w, void* const* out_ranks, int G, int experts_per_rank, int t0, int t1,
                          int topk, int H, cudaStream_t st);
+int moe_push_rows(const int* dst_slot, int T, int topk, int tokens_per_rank, void* const* inbox_ranks, int G, int H,
+                  void** row_ptr, cudaStream_t st);
 int read_device_status(cudaStream_t st, int* out);
 int read_row_status(int* out);  // status word of the row kernels (after the stream was synchronised)
 

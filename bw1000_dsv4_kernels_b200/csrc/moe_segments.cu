@@ -556,6 +556,49 @@ int moe_combine_exchange(const void* const* z_ranks, const int* const* slot_rank
     return check_launch("moe_combine_exchange");
 }
 
+// Where each of this rank's expert output rows has to go when the down GEMM itself delivers them (push
+// instead of the owners' pull): the (token, slot) pair that sits in segment row r = dst_slot[pair] belongs to
+// the rank that owns the token, rank = token / tokens_per_rank, and lands in that rank's inbox at row
+// (token - rank * tokens_per_rank) * topk + slot.
+struct InboxArgs {
+    __nv_bfloat16* inbox[kMaxRanks];
+};
+__global__ void __launch_bounds__(256) moe_push_rows_kernel(InboxArgs a, const int* __restrict__ dst_slot, int pairs,
+                                                            int topk, int tokens_per_rank, int G, int H,
+                                                            void** __restrict__ row_ptr) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= pairs) return;
+    const int r = dst_slot[i];
+    if (r < 0) return;
+    const int t = i / topk, j = i - t * topk;
+    int rank = t / tokens_per_rank;
+    if (rank >= G) rank = G - 1;
+    __nv_bfloat16* base = a.inbox[0];
+#pragma unroll
+    for (int g = 1; g < kMaxRanks; ++g)
+        if (g == rank) base = a.inbox[g];
+    row_ptr[r] = base + ((int64_t)(t - rank * tokens_per_rank) * topk + j) * H;
+}
+
+int moe_push_rows(const int* dst_slot, int T, int topk, int tokens_per_rank, void* const* inbox_ranks, int G, int H,
+                  void** row_ptr, cudaStream_t st) {
+    if (T == 0) return 0;
+    if (G < 1 || G > kMaxRanks) return fail(DSV4_ERR_ARG, "moe_push_rows: 1 to 8 ranks");
+    if (T < 0 || topk <= 0 || tokens_per_rank <= 0 || H <= 0 || (int64_t)T * topk > INT32_MAX)
+        return fail(DSV4_ERR_ARG, "moe_push_rows: bad sizes");
+    if ((int64_t)tokens_per_rank * G < T) return fail(DSV4_ERR_ARG, "moe_push_rows: tokens_per_rank * ranks < T");
+    if (dst_slot == nullptr || inbox_ranks == nullptr || row_ptr == nullptr)
+        return fail(DSV4_ERR_ARG, "moe_push_rows: null pointer");
+    InboxArgs a = {};
+    for (int g = 0; g < G; ++g) {
+        if (inbox_ranks[g] == nullptr) return fail(DSV4_ERR_ARG, "moe_push_rows: null rank pointer");
+        a.inbox[g] = static_cast<__nv_bfloat16*>(inbox_ranks[g]);
+    }
+    const int pairs = T * topk;
+    moe_push_rows_kernel<<<(pairs + 255) / 256, 256, 0, st>>>(a, dst_slot, pairs, topk, tokens_per_rank, G, H, row_ptr);
+    return check_launch("moe_push_rows");
+}
+
 int moe_segments(const int* topk_ids, int T, int topk, int E, int expert_lo, int* offsets, int* src_row,
                  int* dst_slot, cudaStream_t st) {
     if (T < 0 || topk <= 0 || E <= 0) return fail(DSV4_ERR_ARG, "moe_segments: bad sizes");

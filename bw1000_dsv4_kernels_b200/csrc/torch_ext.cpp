@@ -506,6 +506,58 @@ void moe_combine_exchange_stream(std::vector<int64_t> z_ptrs, std::vector<int64_
                                              as_stream(stream_ptr)));
 }
 
+// Grouped GEMM (per-token scales) whose result row r is stored to the address row_ptr[r] (int64 device tensor of
+// R addresses, e.g. rows of other ranks' inboxes in symmetric memory) instead of a dense [R,N] tensor.
+void grouped_gemm_scatter_stream(Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor expert_offsets, Tensor row_ptr,
+                                 int64_t stream_ptr) {
+    check_cuda(A, "A", torch::kInt8);
+    check_cuda(W, "W", torch::kInt8);
+    check_cuda(sa, "sa", torch::kFloat32);
+    check_cuda(sw, "sw", torch::kFloat32);
+    check_cuda(expert_offsets, "expert_offsets", torch::kInt32);
+    check_cuda(row_ptr, "row_ptr", torch::kInt64);
+    check_same_device(A, W, "A/W");
+    check_same_device(A, sa, "A/sa");
+    check_same_device(A, sw, "A/sw");
+    check_same_device(A, expert_offsets, "A/expert_offsets");
+    check_same_device(A, row_ptr, "A/row_ptr");
+    TORCH_CHECK(A.dim() == 2 && W.dim() == 3, "A must be [R,K] and W [E,N,K]");
+    TORCH_CHECK(A.is_contiguous() && W.is_contiguous() && sw.is_contiguous() && sa.is_contiguous() &&
+                expert_offsets.is_contiguous() && row_ptr.is_contiguous(), "all operands must be contiguous");
+    const int R = to_int(A.size(0), "R"), K = to_int(A.size(1), "K");
+    const int E = to_int(W.size(0), "E"), N = to_int(W.size(1), "N");
+    TORCH_CHECK(W.size(2) == K, "A and W disagree on K");
+    TORCH_CHECK(sw.numel() == (int64_t)E * N, "sw must be [E,N]");
+    TORCH_CHECK(sa.numel() == R, "sa must have R entries (per-token scales)");
+    TORCH_CHECK(expert_offsets.numel() == E + 1, "expert_offsets must have E+1 entries");
+    TORCH_CHECK(row_ptr.numel() >= R, "row_ptr must have an address for every row");
+    c10::cuda::CUDAGuard guard(A.device());
+    check_status(launch_grouped_gemm_scatter(A.data_ptr(), W.data_ptr(), sa.data_ptr(), sw.data_ptr(),
+                                             static_cast<const int*>(expert_offsets.data_ptr()),
+                                             reinterpret_cast<void* const*>(row_ptr.data_ptr()), R, E, N, K,
+                                             as_stream(stream_ptr)));
+}
+
+// row_ptr[dst_slot[pair]] = address of the pair's row in the inbox of the rank that owns its token
+void moe_push_rows_stream(Tensor dst_slot, int64_t topk, int64_t tokens_per_rank, std::vector<int64_t> inbox_ptrs,
+                          int64_t H, Tensor row_ptr, int64_t stream_ptr) {
+    check_cuda(dst_slot, "dst_slot", torch::kInt32);
+    check_cuda(row_ptr, "row_ptr", torch::kInt64);
+    check_same_device(dst_slot, row_ptr, "dst_slot/row_ptr");
+    TORCH_CHECK(dst_slot.is_contiguous() && row_ptr.is_contiguous(), "dst_slot and row_ptr must be contiguous");
+    TORCH_CHECK(topk > 0 && dst_slot.numel() % topk == 0, "dst_slot must have T*topk entries");
+    TORCH_CHECK(row_ptr.numel() >= dst_slot.numel(), "row_ptr must have T*topk entries");
+    const size_t G = inbox_ptrs.size();
+    TORCH_CHECK(G >= 1 && G <= 8, "1 to 8 ranks");
+    std::vector<void*> inbox(G);
+    for (size_t g = 0; g < G; ++g) inbox[g] = reinterpret_cast<void*>(inbox_ptrs[g]);
+    c10::cuda::CUDAGuard guard(dst_slot.device());
+    check_status(launch_moe_push_rows(static_cast<const int*>(dst_slot.data_ptr()), to_int(dst_slot.numel() / topk, "T"),
+                                      to_int(topk, "topk"), to_int(tokens_per_rank, "tokens_per_rank"), inbox.data(),
+                                      (int)G, to_int(H, "H"), reinterpret_cast<void**>(row_ptr.data_ptr()),
+                                      as_stream(stream_ptr)));
+}
+
 // w8a8 GEMM written into columns [col0, col0 + N) of an existing bf16 [M, ldc] buffer
 void w8a8_gemm_into_stream(Tensor A, Tensor B, Tensor sa, Tensor sb, Tensor out, int64_t col0, int64_t stream_ptr) {
     const GemmShape g = check_gemm_operands(A, B);
@@ -614,6 +666,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         moe_combine_exchange_stream(z, slot, ids, w, out, epr, t0, t1, H, current_stream_ptr());
     });
     m.def("moe_combine_exchange_stream", &moe_combine_exchange_stream);
+    m.def("grouped_gemm_scatter", [](Tensor A, Tensor W, Tensor sa, Tensor sw, Tensor off, Tensor row_ptr) {
+        grouped_gemm_scatter_stream(A, W, sa, sw, off, row_ptr, current_stream_ptr());
+    });
+    m.def("grouped_gemm_scatter_stream", &grouped_gemm_scatter_stream);
+    m.def("moe_push_rows", [](Tensor dst_slot, int64_t topk, int64_t per, std::vector<int64_t> inbox, int64_t H,
+                              Tensor row_ptr) {
+        moe_push_rows_stream(dst_slot, topk, per, inbox, H, row_ptr, current_stream_ptr());
+    });
+    m.def("moe_push_rows_stream", &moe_push_rows_stream);
     m.def("moe_segments", [](Tensor ids, int64_t E, int64_t lo) {
         return moe_segments_stream(ids, E, lo, current_stream_ptr());
     }, py::arg("topk_ids"), py::arg("num_experts"), py::arg("expert_lo") = 0);

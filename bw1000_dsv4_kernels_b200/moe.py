@@ -165,6 +165,71 @@ class ExchangeW8A8MoE(W8A8MoE):
         return self.out[:t]
 
 
+class PushExchangeW8A8MoE(W8A8MoE):
+    """Expert-parallel forward whose down GEMM delivers its rows itself.
+
+    `ExchangeW8A8MoE` lets the rank that owns a token PULL the token's expert rows from the other ranks
+    after a barrier: loads over NVLink, on the critical path.  Here every rank knows where each of its
+    expert output rows is needed (`moe_push_rows`: the inbox of the token's owner, at row
+    (token - t0) * topk + slot) and the down GEMM stores each result row straight there
+    (`grouped_gemm_scatter`), as posted peer stores, while it is still streaming weights.  After the barrier
+    the owner's combine reads its own memory only, sums in slot order -- the single-GPU arithmetic and bits
+    -- and pushes the finished row into every rank's output as before.  No NCCL on the data path.
+    """
+
+    def __init__(self, w13, w13_scale, w2, w2_scale, num_experts: int, rank: int, world: int, t_max: int, topk: int,
+                 device, group_scaled: bool = True, process_group=None):
+        per = num_experts // world
+        assert per * world == num_experts and w13.shape[0] == per
+        super().__init__(w13, w13_scale, w2, w2_scale, num_experts, rank * per, group_scaled, process_group)
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        self.rank, self.world, self.t_max, self.topk = rank, world, t_max, topk
+        group = process_group if process_group is not None else dist.group.WORLD
+        rows = -(-t_max // world) * topk
+        self.inbox = symm_mem.empty((rows, self.hidden), dtype=torch.bfloat16, device=device)
+        self.out = symm_mem.empty((t_max, self.hidden), dtype=torch.bfloat16, device=device)
+        self.handle = symm_mem.rendezvous(self.inbox, group=group)
+        self.inbox_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.out_ptrs = [int(p) for p in symm_mem.rendezvous(self.out, group=group).buffer_ptrs]
+        self.row_ptr = torch.zeros(t_max * topk, dtype=torch.int64, device=device)
+        self.pair_index = torch.arange(t_max * topk, dtype=torch.int32, device=device)
+        self._slot_for = {}
+
+    def _local_slots(self, t: int, t0: int):
+        """slot table for the combine: pair (token, j) of an own token sits at inbox row (token - t0) * topk + j"""
+        key = (t, t0)
+        if key not in self._slot_for:
+            self._slot_for[key] = (self.pair_index[: t * self.topk] - t0 * self.topk).contiguous()
+        return self._slot_for[key]
+
+    def forward(self, x, topk_ids, topk_w, keep_trace: bool = False):
+        t = x.shape[0]
+        assert t <= self.t_max and topk_ids.shape[1] == self.topk, "batch larger than the symmetric buffers"
+        ext = _ext()
+        inter = self.inter
+        t0, t1 = token_range(self.rank, self.world, t)
+        per = -(-t // self.world)
+        if self.group_scaled:
+            q, s = ext.per_token_group_quant_int8(x, GROUP)
+        else:
+            q, s = ext.per_token_quant_int8(x)
+        off, src_row, dst_slot = ext.moe_segments(topk_ids, self.e_local, self.expert_lo)
+        ext.moe_push_rows(dst_slot, self.topk, per, self.inbox_ptrs, self.hidden, self.row_ptr)
+        valid = off[self.e_local:]
+        a_q, a_s = ext.gather_rows(q, src_row, s, valid)
+        y = ext.grouped_gemm(a_q, self.w13, a_s, self.w13_scale, off)
+        h_q, h_s = ext.silu_mul_quant_rows(y[:, :inter], y[:, inter:], valid)
+        ext.grouped_gemm_scatter(h_q, self.w2, h_s, self.w2_scale, off, self.row_ptr)
+        self.handle.barrier(channel=0)      # every rank's rows have been delivered
+        inbox = [self.inbox_ptrs[self.rank]] * self.world
+        slots = [self._local_slots(t, t0).data_ptr()] * self.world
+        ext.moe_combine_exchange(inbox, slots, topk_ids, topk_w, self.out_ptrs, self.num_experts // self.world,
+                                 t0, t1, self.hidden)
+        self.handle.barrier(channel=1)      # every rank's output rows have landed everywhere, inboxes are free again
+        return self.out[:t]
+
+
 def route(router_logits: torch.Tensor, topk: int):
     """Router top-k on the device: fp32 logits [T,E] -> (ids int32 [T,topk], weights fp32 [T,topk] =
     softmax over the selected logits).  Ties go to the lower expert index."""

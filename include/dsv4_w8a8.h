@@ -239,6 +239,22 @@ DSV4_API int launch_moe_combine_exchange(const void* const* z_ranks, const int* 
                        const int* topk_ids, const float* topk_w, void* const* out_ranks, int num_ranks,
                        int experts_per_rank, int t0, int t1, int topk, int H, dsv4_stream_t stream);
 
+/* Expert-parallel down projection that delivers its rows itself (no reference counterpart, as above).
+ * launch_grouped_gemm with per-token scales, except that row r of the result is stored to row_ptr[r]
+ * (device array of R device addresses, each a bf16 row of N elements, 2-byte aligned, possibly in another
+ * GPU's memory mapped into this process) instead of C + r * N.  With the table that
+ * launch_moe_push_rows builds, every expert output row lands in the inbox of the rank that owns its token
+ * while the GEMM is still streaming weights, so the owners' combine reads local memory only. */
+DSV4_API int launch_grouped_gemm_scatter(const void* A, const void* W, const void* sa, const void* sw,
+                       const int* expert_offsets, void* const* row_ptr, int R, int E, int N, int K,
+                       dsv4_stream_t stream);
+/* row_ptr[dst_slot[t*topk+j]] = inbox_ranks[g] + ((t - g*tokens_per_rank)*topk + j) * H elements, g = the
+ * rank that owns token t (t / tokens_per_rank), for every pair whose dst_slot is not -1.  inbox_ranks is a
+ * HOST array of num_ranks device pointers (bf16 [tokens_per_rank*topk, H] each); row_ptr is a device array
+ * with one entry per segment row of this rank. */
+DSV4_API int launch_moe_push_rows(const int* dst_slot, int T, int topk, int tokens_per_rank,
+                       void* const* inbox_ranks, int num_ranks, int H, void** row_ptr, dsv4_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

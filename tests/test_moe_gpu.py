@@ -191,6 +191,67 @@ def test_moe_combine_exchange_on_one_gpu(ext, world, t, topk):
     assert torch.equal(outs[0].cpu().view(torch.int16), ref_o.view(torch.int16)), "oracle"
 
 
+@pytest.mark.parametrize("world,t,topk", [(2, 64, 2), (4, 131, 4), (8, 40, 8)])
+def test_moe_down_gemm_pushes_rows_to_the_owners_on_one_gpu(ext, world, t, topk):
+    # the push form of the expert-parallel forward, every "rank's" inbox on one GPU: each rank's down GEMM
+    # stores its rows into the inbox of the token's owner (moe_push_rows + grouped_gemm_scatter); the owner's
+    # combine then reads its own inbox only.  Same bits as the single-rank forward.
+    from bw1000_dsv4_kernels_b200 import moe
+    h, e, inter = 512, 24, 256
+    if e % world:
+        e = world * 3
+    full = wl.moe_inputs(t, h, e, inter, topk, seed=33)
+    whole = moe.W8A8MoE(full.w13.cuda(), full.w13_scale.cuda(), full.w2.cuda(), full.w2_scale.cuda(), e)
+    ids, w = full.topk_ids.cuda(), full.topk_w.cuda()
+    ref = whole.forward(full.x.cuda(), ids, w)
+    per = -(-t // world)
+    inboxes = [torch.full((per * topk, h), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    for r in range(world):
+        lo, hi = moe.expert_range(r, world, e)
+        part_in = wl.moe_inputs(t, h, e, inter, topk, seed=33, expert_lo=lo, expert_hi=hi)
+        layer = moe.W8A8MoE(part_in.w13.cuda(), part_in.w13_scale.cuda(), part_in.w2.cuda(), part_in.w2_scale.cuda(),
+                            e, expert_lo=lo)
+        layer.local_partial(part_in.x.cuda(), ids, w, out_f32=True, keep_trace=True)
+        tr = layer.last_trace
+        row_ptr = torch.zeros(t * topk, dtype=torch.int64, device="cuda")
+        ext.moe_push_rows(tr.dst_slot, topk, per, [b.data_ptr() for b in inboxes], h, row_ptr)
+        # the table against its definition
+        slot = tr.dst_slot.cpu()
+        want = torch.zeros(t * topk, dtype=torch.int64)
+        for i in range(t * topk):
+            if slot[i] >= 0:
+                tok, j = divmod(i, topk)
+                g = min(tok // per, world - 1)
+                want[slot[i]] = inboxes[g].data_ptr() + ((tok - g * per) * topk + j) * h * 2
+        rows = int(tr.offsets[-1])
+        assert torch.equal(row_ptr.cpu()[:rows], want[:rows])
+        ext.grouped_gemm_scatter(tr.h_q, layer.w2, tr.h_s, layer.w2_scale, tr.offsets, row_ptr)
+    torch.cuda.synchronize()
+    outs = [torch.full((t, h), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    pair = torch.arange(t * topk, dtype=torch.int32, device="cuda")
+    for r in range(world):
+        t0, t1 = moe.token_range(r, world, t)
+        local = (pair - t0 * topk).contiguous()
+        ext.moe_combine_exchange([inboxes[r].data_ptr()] * world, [local.data_ptr()] * world, ids, w,
+                                 [o.data_ptr() for o in outs], e // world, t0, t1, h)
+    for r in range(world):
+        assert torch.equal(outs[r].view(torch.int16), ref.view(torch.int16)), f"rank {r}'s output buffer"
+
+
+def test_grouped_gemm_scatter_rejects_group_scales_and_null(cabi):
+    import ctypes
+    a = torch.zeros((16, 128), dtype=torch.int8, device="cuda")
+    wgt = torch.zeros((1, 128, 128), dtype=torch.int8, device="cuda")
+    sa = torch.ones(16, device="cuda")
+    sw = torch.ones((1, 128), device="cuda")
+    off = torch.tensor([0, 16], dtype=torch.int32, device="cuda")
+    lib = cabi.lib()
+    p = lambda x: ctypes.c_void_p(x.data_ptr())
+    rc = lib.launch_grouped_gemm_scatter(p(a), p(wgt), p(sa), p(sw), p(off), ctypes.c_void_p(0), 16, 1, 128, 128,
+                                         ctypes.c_void_p(0))
+    assert rc != 0 and "row_ptr" in cabi.last_error()
+
+
 def test_moe_combine_exchange_rejects_bad_arguments(ext):
     ids = torch.zeros((4, 2), dtype=torch.int32, device="cuda")
     w = torch.zeros((4, 2), dtype=torch.float32, device="cuda")

@@ -67,6 +67,13 @@ def _worker(rank, world, port, ret):
             out_x = ex.forward(part.x, part.topk_ids, part.topk_w)
             torch.cuda.synchronize()
             assert torch.equal(out_x.view(torch.int16), ref_m.view(torch.int16)), "fused EP combine"
+        # the push form: the down GEMM stores every row into the inbox of the token's owner
+        push = moe.PushExchangeW8A8MoE(part.w13, part.w13_scale, part.w2, part.w2_scale, e, rank, world, t_max=t,
+                                       topk=topk, device=dev)
+        for _ in range(3):
+            out_p = push.forward(part.x, part.topk_ids, part.topk_w)
+            torch.cuda.synchronize()
+            assert torch.equal(out_p.view(torch.int16), ref_m.view(torch.int16)), "EP forward with pushed rows"
         ret[rank] = "ok"
     except Exception as exc:  # pragma: no cover
         import traceback
