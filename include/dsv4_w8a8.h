@@ -241,8 +241,9 @@ DSV4_API int launch_moe_combine_exchange(const void* const* z_ranks, const int* 
 
 /* Expert-parallel down projection that delivers its rows itself (no reference counterpart, as above).
  * launch_grouped_gemm with per-token scales, except that row r of the result is stored to row_ptr[r]
- * (device array of R device addresses, each a bf16 row of N elements, 2-byte aligned, possibly in another
- * GPU's memory mapped into this process) instead of C + r * N.  With the table that
+ * (device array of R device addresses, each a bf16 row of N elements, possibly in another GPU's memory
+ * mapped into this process; 16-byte aligned rows leave in 256-byte segments, others element by element)
+ * instead of C + r * N.  With the table that
  * launch_moe_push_rows builds, every expert output row lands in the inbox of the rank that owns its token
  * while the GEMM is still streaming weights, so the owners' combine reads local memory only. */
 DSV4_API int launch_grouped_gemm_scatter(const void* A, const void* W, const void* sa, const void* sw,
