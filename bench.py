@@ -794,6 +794,20 @@ def run_single_kernel(args):
             sa = wl.channel_scales((E * rows,), device=dev, seed=2)
         fn = lambda i: ext.grouped_gemm(A, W[i % 2], sa, sw, off)
         work = {"ops": 2.0 * E * rows * N2 * K, "bytes": E * N2 * K + E * rows * (K + 2 * N2)}
+    elif args.kernel == "grouped_scatter":
+        # the down projection that delivers its rows itself: 16 experts x `m` rows (default 128), N=7168, K=2048,
+        # every result row stored at its own address (here: the rows of one local buffer in reverse order)
+        rows = 128 if m == M_ROWS else m
+        E, N2, K2 = 16, K, wl.MOE_INTER
+        off = torch.arange(0, (E + 1) * rows, rows, dtype=torch.int32, device=dev)
+        A = wl.int8_weights((E * rows, K2), device=dev, seed=1)
+        W = [wl.int8_weights((E, N2, K2), device=dev, seed=10 + i) for i in range(4)]
+        sw = wl.channel_scales((E, N2), device=dev, seed=3)
+        sa = wl.channel_scales((E * rows,), device=dev, seed=2)
+        inbox = torch.empty((E * rows, N2), dtype=torch.bfloat16, device=dev)
+        row_ptr = (inbox.data_ptr() + torch.arange(E * rows - 1, -1, -1, dtype=torch.int64, device=dev) * (N2 * 2)).contiguous()
+        fn = lambda i: ext.grouped_gemm_scatter(A, W[i % 4], sa, sw, off, row_ptr)
+        work = {"ops": 2.0 * E * rows * N2 * K2, "bytes": E * N2 * K2 + E * rows * (K2 + 2 * N2)}
     elif args.kernel == "ptgq":
         xs = [wl.randn_bf16((m, K), device=dev, seed=i) for i in range(nsets)]
         fn = lambda i: ext.per_token_group_quant_int8(xs[i % nsets], 128)
@@ -869,7 +883,7 @@ def run_single_kernel(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default=None,
-                    help="run one kernel only: gemm, gemm_tp, gemm_down, gemm_allgather, grouped, grouped_gs, "
+                    help="run one kernel only: gemm, gemm_tp, gemm_down, gemm_allgather, grouped, grouped_gs, grouped_scatter, "
                          "add_rmsnorm_quant, silu_mul_quant, ptq, ptgq, rmsnorm, silu_and_mul, moe_topk, moe_segments, "
                          "gather_rows, moe_combine, moe_combine_exchange")
     ap.add_argument("--m", type=int, default=M_ROWS, help="rows for --kernel")
