@@ -317,6 +317,21 @@ gemm_i8_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                 // token scales of the item -> shared memory (everybody reads all of them)
                 asm volatile("bar.sync 1, %0;" ::"n"(kDrain) : "memory");   // the previous item's readers are done
                 for (int i = dtid; i < kWtChunk; i += kDrain) tok_scale[i] = i < it.cnt ? __ldg(p.sa + it.row0 + i) : 0.0f;
+                // STAGED: where this thread's rows go (rows dtid / 16, + 8, + 16, ...), asked for now so that the
+                // loads are long done when the tile is written out
+                constexpr int kRowsPerThread = STAGED ? kWtChunk / (kDrain / 16) : 1;
+                __nv_bfloat16* dstp[kRowsPerThread];
+                if constexpr (STAGED) {
+#pragma unroll
+                    for (int k = 0; k < kRowsPerThread; ++k) {
+                        const int c = (dtid >> 4) + k * (kDrain / 16);
+                        dstp[k] = nullptr;
+                        if (c < it.cnt)
+                            dstp[k] = p.row_ptr != nullptr
+                                ? reinterpret_cast<__nv_bfloat16*>(__ldg(reinterpret_cast<const unsigned long long*>(p.row_ptr) + it.row0 + c))
+                                : static_cast<__nv_bfloat16*>(p.C) + (int64_t)(it.row0 + c) * p.ldc;
+                    }
+                }
                 const uint32_t b = blk % kWtAccs;
                 bool go = ptx::mbar_wait_bounded(acc_full_bar(b), (blk / kWtAccs) & 1u, p.wait_limit_ns) && !*abort_flag;
                 go = ptx::barrier_and<1, kDrain>(go);                        // also publishes the scales
@@ -365,10 +380,11 @@ gemm_i8_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                     asm volatile("bar.sync 2, %0;" ::"n"(kDrain) : "memory");
                     const int seg = dtid & 15;                       // 16-byte piece of the 256-byte row segment
                     const int nn = it.n0 + seg * 8;
-                    for (int c = dtid >> 4; c < it.cnt; c += kDrain / 16) {
-                        __nv_bfloat16* dst = p.row_ptr != nullptr
-                            ? reinterpret_cast<__nv_bfloat16*>(__ldg(reinterpret_cast<const unsigned long long*>(p.row_ptr) + it.row0 + c))
-                            : static_cast<__nv_bfloat16*>(p.C) + (int64_t)(it.row0 + c) * p.ldc;
+#pragma unroll
+                    for (int k = 0; k < kRowsPerThread; ++k) {
+                        const int c = (dtid >> 4) + k * (kDrain / 16);
+                        __nv_bfloat16* dst = dstp[k];
+                        if (dst == nullptr) continue;
                         const uint4 v = *reinterpret_cast<const uint4*>(out_tile + c * 128 + seg * 8);
                         if (nn + 8 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
                             *reinterpret_cast<uint4*>(dst + nn) = v;
