@@ -221,6 +221,29 @@ def test_grouped_gemm_matches_oracle(cabi, ext, seg_lens, n, k):
     _check_bf16(out2, ref, "operator")
 
 
+@pytest.mark.parametrize("seg_lens,n,k,shift", [
+    ([5, 0, 300, 128, 1, 0, 77], 512, 384, 0),      # 16-byte aligned rows: 256-byte segments
+    ([130] * 4, 1000, 512, 0),                       # N ends inside a 16-byte piece of the last tile
+    ([64, 200, 17], 200, 7168, 1),                   # rows aligned to 2 bytes only: element stores
+])
+def test_grouped_gemm_with_row_destinations(cabi, ext, seg_lens, n, k, shift):
+    # every result row is stored at its own address: here the rows of a wider buffer in reverse order
+    A, W, sa, sw, off = _grouped_case(seg_lens, n, k, seed=len(seg_lens) + n + k)
+    ref = oracle.grouped_gemm(A, W, sa, sw, off)
+    r = A.shape[0]
+    width = n + 24
+    buf = torch.full((r, width), float("nan"), dtype=torch.bfloat16, device="cuda")
+    rows = torch.arange(r - 1, -1, -1, dtype=torch.int64, device="cuda")
+    row_ptr = (buf.data_ptr() + rows * (width * 2) + 2 * shift).contiguous()
+    ext.grouped_gemm_scatter(A.cuda(), W.cuda(), sa.cuda(), sw.cuda(), off.cuda(), row_ptr)
+    torch.cuda.synchronize()
+    assert cabi.device_status() == 0
+    got = buf.flip(0)[:, shift:shift + n].contiguous()
+    _check_bf16(got, ref, "row destinations")
+    untouched = torch.cat([buf[:, :shift], buf[:, shift + n:]], dim=1)
+    assert bool(torch.isnan(untouched.float()).all()), "stores outside the rows' N elements"
+
+
 @pytest.mark.parametrize("seg_lens,n,k", [
     ([128, 128], 256, 256),
     ([5, 0, 300, 128, 1, 0, 77], 520, 384),
