@@ -849,6 +849,15 @@ def run_single_kernel(args):
                 fn = lambda i: ext.moe_combine_exchange([zs[i % 2].data_ptr()], [dst_slot.data_ptr()], ids, w,
                                                         [outb.data_ptr()], E, 0, T, H)
             work = {"bytes": 2 * T * topk * H + 2 * T * H}
+    elif args.kernel in ("moe_ffn", "moe_ffn_per_token"):
+        # the whole MoE FFN of the configuration on one GPU (256 experts, 4096 tokens, top-8): nine launches per call
+        from bw1000_dsv4_kernels_b200 import moe
+        inp = wl.moe_inputs(device=dev, seed=0)
+        layer = moe.W8A8MoE(inp.w13, inp.w13_scale, inp.w2, inp.w2_scale, wl.MOE_EXPERTS,
+                            group_scaled=(args.kernel == "moe_ffn"))
+        fn = lambda i: layer.forward(inp.x, inp.topk_ids, inp.topk_w)
+        rows = wl.MOE_TOKENS * wl.MOE_TOPK
+        work = {"ops": 2.0 * rows * 3 * wl.MOE_INTER * K, "bytes": wl.MOE_EXPERTS * 3 * wl.MOE_INTER * K}
     elif args.kernel == "gemm_allgather":
         # the CTA-pair GEMM with the fused all-gather epilogue (TMA tile stores), two local buffers
         # standing in for this rank's and one peer's output
@@ -885,7 +894,7 @@ def main():
     ap.add_argument("--kernel", default=None,
                     help="run one kernel only: gemm, gemm_tp, gemm_down, gemm_allgather, grouped, grouped_gs, grouped_scatter, "
                          "add_rmsnorm_quant, silu_mul_quant, ptq, ptgq, rmsnorm, silu_and_mul, moe_topk, moe_segments, "
-                         "gather_rows, moe_combine, moe_combine_exchange")
+                         "gather_rows, moe_combine, moe_combine_exchange, moe_ffn (group scales), moe_ffn_per_token")
     ap.add_argument("--m", type=int, default=M_ROWS, help="rows for --kernel")
     ap.add_argument("--graph", action="store_true", help="with --kernel: also time CUDA-graph replays")
     ap.add_argument("--gpus", type=int, default=1)
