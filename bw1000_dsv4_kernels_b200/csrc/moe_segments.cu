@@ -101,7 +101,8 @@ __global__ void __launch_bounds__(kSegThreads) seg_scatter_kernel(const int* __r
 
 
 // ---- chunked form (R >= 1024 pairs, E <= 1024): one warp per chunk -------------------------
-// The chunk length is 256 pairs for up to 64 experts (short serial loops in the scatter), else 1024.
+// The chunk length is 256 pairs for up to 64 experts (short serial loops in the scatter), 512 up to 512
+// experts, else 1024.
 // count   : warp b builds the histogram of its chunk in shared memory and parks it in the
 //           chunk's own stretch of dst_slot (dst_slot[chunk_begin + e], e < E <= chunk length)
 // scan    : one warp (few experts) or one thread (many) per expert turns the per-chunk counts of
@@ -611,7 +612,7 @@ int moe_segments(const int* topk_ids, int T, int topk, int E, int expert_lo, int
         // few experts (an expert-parallel rank): short chunks, one warp per expert in the scan; many
         // experts: long chunks, one thread per expert
         const bool few = E <= 64;
-        const int chunk = few ? 256 : kChunk;
+        const int chunk = few ? 256 : (E <= 512 ? 512 : kChunk);   // a chunk parks E counts in its own stretch: E <= chunk
         const int nchunks = R / chunk;
         seg_chunk_count_kernel<<<nchunks, 32, 0, st>>>(topk_ids, R, E, chunk, expert_lo, dst_slot);
         if (few)
